@@ -19,6 +19,7 @@ class NormSpec:
     eps: float
     kind: str = "rmsnorm"
     tensor: str = "weight"                  # local name of the weight behind the norm's prefix ('' : the prefix itself)
+    offset: float = 0.0                     # the stored weight is added to this (1.0: a weight stored around zero)
 
 
 @dataclass(frozen=True)
@@ -45,6 +46,11 @@ class AttentionSpec:
     bias: bool = False                      # bias on the q, k, v and o projections
     window: Optional[int] = None            # None: all keys; n: the last n keys (itself included)
     kind: str = "attention"
+    v_dim: Optional[int] = None             # size of a value head (None: head_dim)
+    head_sinks: bool = False                # a learned logit per query head joins the softmax denominator, without a value
+    head_gate: bool = False                 # head h's output is multiplied by sigmoid(W_g x)_h, one number per head
+    shares_cache: bool = False              # no key/value tensors: the layer reads the keys and values another layer caches
+    short_names: bool = False               # tensors are 'q', 'k', 'v', 'o', 'q.norm', 'k.norm', 'sink', 'g'
 
     @property
     def q_size(self) -> int:
@@ -54,6 +60,10 @@ class AttentionSpec:
     def kv_size(self) -> int:
         return self.num_kv_heads * self.head_dim
 
+    @property
+    def value_dim(self) -> int:
+        return self.head_dim if self.v_dim is None else self.v_dim
+
 
 @dataclass(frozen=True)
 class GatedMLPSpec:
@@ -62,6 +72,7 @@ class GatedMLPSpec:
     intermediate_size: int
     activation: str = "silu"
     kind: str = "gated_mlp"
+    names: Tuple[str, str, str] = ("gate_proj.weight", "up_proj.weight", "down_proj.weight")    # gate, up, down
 
 
 @dataclass(frozen=True)
@@ -113,6 +124,14 @@ class ExpertsSpec:
     activation: str = "relu_squared"
     weight_eps: float = 1e-20
     kind: str = "experts"
+    # activation 'clamped_glu': an expert is down(g * sigmoid(glu_alpha * g) * (u + 1)) with g = min(gate h, glu_limit)
+    # and u = clamp(up h, -glu_limit, glu_limit)
+    glu_limit: float = 0.0
+    glu_alpha: float = 1.702
+    identity_experts: int = 0               # the router has this many outputs more: experts whose output is their input
+    score_correction: bool = False          # a learned number per router output is added to the scores for the CHOICE only
+    renormalize: bool = True                # False: the weights are the chosen scores themselves, not divided by their sum
+    router_input: str = "stream"            # 'stream': the router reads the float32 residual; 'input': the sublayer's input
 
 
 @dataclass(frozen=True)
@@ -151,6 +170,43 @@ class GatedLinearAttentionSpec:
     norm_eps: float
     gate_rank: int = 0
     kind: str = "gated_linear_attention"
+
+
+@dataclass(frozen=True)
+class RetentionSpec:
+    """Linear attention with a fixed decay per head and no softmax or denominator: S <- decays[h] S + k v^T,
+    o = S^T q per head, q and k rotated by their positions (``position``), k scaled by ``key_dim`` ** -0.5 after the
+    rotation. Each head's o is divided by its root mean square (no weight), the heads side by side are multiplied by
+    silu(W_g h) and projected."""
+    hidden_size: int
+    num_heads: int
+    key_dim: int
+    value_dim: int
+    decays: Tuple[float, ...]
+    position: PositionSpec
+    norm_eps: float
+    kind: str = "retention"
+
+
+@dataclass(frozen=True)
+class ChannelDeltaSpec:
+    """The gated delta rule with a decay per head and key channel. q and k (``num_kv_heads`` heads of ``key_dim``) and v
+    (``num_heads`` heads of ``value_dim``) pass a causal convolution of ``conv_taps`` taps per channel and silu; q and
+    k become unit vectors per head (x / sqrt(sum x^2 + ``unit_eps``)), q also times key_dim ** -0.5;
+    beta = sigmoid(W_b h) per head; g = exp(-exp(A_log[h]) softplus(W_a2 W_a1 h + dt_bias)) per head and key channel;
+    S <- diag(g) S, u = beta (v - S^T k), S <- S + k u^T, o = S^T q. Each head's o is divided by its root mean
+    square, weighted (one weight of value_dim entries for all heads), gated by sigmoid(W_g2 W_g1 h) and projected.
+    ``gate_rank``: the inner size of the two-step projections; 0: whatever the checkpoint's tensors have."""
+    hidden_size: int
+    num_heads: int
+    num_kv_heads: int
+    key_dim: int
+    value_dim: int
+    conv_taps: int
+    norm_eps: float
+    unit_eps: float = 1e-6
+    gate_rank: int = 0
+    kind: str = "channel_delta"
 
 
 @dataclass(frozen=True)

@@ -44,6 +44,9 @@ struct AttnParams {
     float scale_log2;              // softmax scale times log2(e)
     int has_sink;                  // the softmax denominator holds one more term 2^sink_log2 that has no value
     float sink_log2, out_scale;    // out_scale multiplies the output before its rounding
+    const float* head_sinks;         // float32 [query heads]: a sink's logit per head in place of sink_log2 (or null)
+    const __nv_bfloat16* gate;       // rows of ld_gate, first column gate_off: out *= sigmoid(gate[token][head]) (or null)
+    int ld_gate, gate_off;
     int* status;
 };
 
@@ -431,9 +434,10 @@ __global__ void __launch_bounds__(THREADS) decode_attention_kernel(const __grid_
                     l_all += f * mbuf[((size_t)w4 * group + hrow) * LDW + D + 1];
                 }
                 if (item.cta0 == item.cta1) {                      // the pair lies inside this run: this is its result
-                    const float l_fin = p.has_sink ? l_all + exp2f(p.sink_log2 - m_all) : l_all;
-                    p.out[((size_t)item.row * p.hq + (size_t)item.kvh * group + hrow) * D + d] =
-                        __float2bfloat16_rn(l_fin > 0.f ? acc * p.out_scale / l_fin : 0.f);
+                    const int head = item.kvh * group + hrow;
+                    const float l_fin = p.has_sink ? l_all + exp2f(ti_sink_log2(p, head) - m_all) : l_all;
+                    p.out[((size_t)item.row * p.hq + head) * D + d] =
+                        __float2bfloat16_rn(l_fin > 0.f ? acc * ti_head_out_scale(p, item.row, head) / l_fin : 0.f);
                 } else {
                     const size_t slot = (size_t)item.slot * group + hrow;
                     __stcg(p.part_o + slot * D + d, acc);
@@ -489,8 +493,9 @@ __global__ void __launch_bounds__(THREADS) decode_attention_kernel(const __grid_
             float f[4], l_all = 0.f;
 #pragma unroll
             for (int w4 = 0; w4 < 4; ++w4) { f[w4] = exp2f(mw[w4] - m_use); l_all += f[w4] * lw[w4]; }
-            const float l_fin = p.has_sink ? l_all + exp2f(p.sink_log2 - m_all) : l_all;       // used where the result is final
-            const float inv = l_fin > 0.f ? p.out_scale / l_fin : 0.f;
+            const int head = item.kvh * group + hrow;
+            const float l_fin = p.has_sink ? l_all + exp2f(ti_sink_log2(p, head) - m_all) : l_all;       // used where the result is final
+            const float inv = l_fin > 0.f ? (item.cta0 == item.cta1 ? ti_head_out_scale(p, item.row, head) : 1.f) / l_fin : 0.f;
 #pragma unroll
             for (int nb = 0; nb < D / 8; ++nb) {               // every block, so that the accumulator's index is a constant
                 if (nb / NB_OWN != warp) continue;
@@ -578,8 +583,8 @@ __global__ void decode_merge_kernel(const AttnParams p) {
         }
         m_run = m_new;
     }
-    if (p.has_sink) l_all += exp2f(p.sink_log2 - m_run);
-    p.out[((size_t)rt.row * p.hq + h) * D + d] = __float2bfloat16_rn(l_all > 0.f ? acc * p.out_scale / l_all : 0.f);
+    if (p.has_sink) l_all += exp2f(ti_sink_log2(p, h) - m_run);
+    p.out[((size_t)rt.row * p.hq + h) * D + d] = __float2bfloat16_rn(l_all > 0.f ? acc * ti_head_out_scale(p, rt.row, h) / l_all : 0.f);
 }
 
 template <typename K>
@@ -661,12 +666,14 @@ TI_API long long ti_attention_decode_scratch_floats(int num_rows, int hq, int hk
 // positions before each row's own are read before the kernels wait for the work ahead of them in the stream:
 // they must be complete when the call is made, not results of the kernels launched just before (those may
 // write q and the keys and values at the rows' own positions). Calls that share the scratch must not overlap.
-// has_sink: exp(sink) joins every softmax denominator without a value; out_scale: a factor on the output.
+// has_sink: exp(sink) joins every softmax denominator without a value; out_scale: a factor on the output;
+// head_sinks, gate: a sink per query head, and a sigmoid gate per (token, query head) on the output (or null).
 TI_API int ti_attention_decode_sink_bf16(void* out, const void* q, const void* kv_cache, float* scratch, long long scratch_floats,
                                          const int* rows, int num_rows, const int* positions, const int* token_seq,
                                          const int* block_table, int max_blocks, int hq, int hkv, int d, int page_size,
                                          int num_pages, float scale, int window, int max_context, int has_sink, float sink,
-                                         float out_scale, int* status, cudaStream_t stream) {
+                                         float out_scale, const float* head_sinks, const void* gate, int ld_gate, int gate_off,
+                                         int* status, cudaStream_t stream) {
     if (check_shape(hq, hkv, d, page_size, "attention_decode")) return -1;
     TI_REQUIRE(num_rows >= 0 && num_rows <= 65535 && max_context > 0, "attention_decode: bad sizes");
     if (num_rows == 0) return 0;
@@ -684,7 +691,8 @@ TI_API int ti_attention_decode_sink_bf16(void* out, const void* q, const void* k
     p.rows = rows; p.positions = positions; p.token_seq = token_seq; p.block_table = block_table;
     p.max_blocks = max_blocks; p.hq = hq; p.hkv = hkv; p.page_size = page_size; p.num_pages = num_pages;
     p.window = window; p.scale_log2 = scale * 1.4426950408889634f; p.status = status;
-    p.has_sink = has_sink ? 1 : 0; p.sink_log2 = sink * 1.4426950408889634f; p.out_scale = out_scale;
+    p.has_sink = has_sink || head_sinks ? 1 : 0; p.sink_log2 = sink * 1.4426950408889634f; p.out_scale = out_scale;
+    p.head_sinks = head_sinks; p.gate = (const __nv_bfloat16*)gate; p.ld_gate = ld_gate; p.gate_off = gate_off;
     p.num_rows = num_rows; p.num_ctas = ctas;
     if (d == 128 && decode_form(group) == 2) {
         const int bytes = Smem<128>::decode_bytes(group, 2 * STAGES);
@@ -730,7 +738,7 @@ TI_API int ti_attention_decode_bf16(void* out, const void* q, const void* kv_cac
                                     cudaStream_t stream) {
     return ti_attention_decode_sink_bf16(out, q, kv_cache, scratch, scratch_floats, rows, num_rows, positions, token_seq,
                                          block_table, max_blocks, hq, hkv, d, page_size, num_pages, scale, window, max_context,
-                                         0, 0.f, 1.f, status, stream);
+                                         0, 0.f, 1.f, nullptr, nullptr, 0, 0, status, stream);
 }
 
 // ------------------------------------------------------------------------------------------------

@@ -61,6 +61,9 @@ struct PairParams {
     float scale_log2;
     int has_sink;                    // the softmax denominator holds one more term 2^sink_log2 that has no value
     float sink_log2, out_scale;      // out_scale multiplies the output before its rounding
+    const float* head_sinks;         // float32 [query heads]: a sink's logit per head in place of sink_log2 (or null)
+    const __nv_bfloat16* gate;       // rows of ld_gate, first column gate_off: out *= sigmoid(gate[token][head]) (or null)
+    int ld_gate, gate_off;
     int* status;
 };
 
@@ -398,9 +401,9 @@ prefill_attention_pair_kernel(const __grid_constant__ CUtensorMap q_map, const _
         if (ok && num_x > 0) {
             if (mbar_wait(o_full(x), (num_x - 1) & 1u, abort_flag, p.status, 47)) {
                 tmem_fence_after();
-                const float l_all = p.has_sink ? l_run + ex2(p.sink_log2 - m_ref) : l_run;      // every score far below the sink: inf, 0
-                const float inv = l_all > 0.f ? p.out_scale / l_all : 0.f;
+                const float l_all = p.has_sink ? l_run + ex2(ti_sink_log2(p, head) - m_ref) : l_run;      // every score far below the sink: inf, 0
                 const int rows_x = min(QM, nrows - x * QM);
+                const float inv = l_all > 0.f ? (r < rows_x ? ti_head_out_scale(p, (size_t)(row0 + x * QM + r), head) : 1.f) / l_all : 0.f;
                 __nv_bfloat16* dst = p.out + ((size_t)(row0 + x * QM + r) * p.hq + head) * D;
                 uint32_t orow[32];
 #pragma unroll
@@ -439,11 +442,13 @@ TI_API int ti_attention_prefill_pair_rows() { return 2 * QM; }
 // Prefill attention on tcgen05, two query tiles a CTA. `tiles`: num_tiles int4 {request index in the step,
 // first flat row, rows (<= 256), position of the first row}, every tile inside one request's portion.
 // q [T, Hq, D], out [T, Hq * D], kv_cache [2, num_pages, Hkv, page_size, D]; page_size 16, 32 or a multiple of 64.
-// has_sink: exp(sink) joins every softmax denominator without a value; out_scale: a factor on the output.
+// has_sink: exp(sink) joins every softmax denominator without a value; out_scale: a factor on the output;
+// head_sinks, gate: a sink per query head, and a sigmoid gate per (token, query head) on the output (or null).
 TI_API int ti_attention_prefill_pair_sink_bf16(void* out, const void* q, const void* kv_cache, const int* tiles, int num_tiles,
                                                int num_tokens, const int* block_table, int max_blocks, int hq, int hkv, int d,
                                                int page_size, int num_pages, float scale, int window, int has_sink,
-                                               float sink, float out_scale, int* status, cudaStream_t stream) {
+                                               float sink, float out_scale, const float* head_sinks, const void* gate,
+                                               int ld_gate, int gate_off, int* status, cudaStream_t stream) {
     TI_REQUIRE(d == 64 || d == 128, "attention_prefill_pair: head_dim %d is not 64 or 128", d);
     TI_REQUIRE(hq > 0 && hkv > 0 && hq % hkv == 0, "attention_prefill_pair: bad head counts");
     TI_REQUIRE(num_tiles <= 65535, "attention_prefill_pair: more than 65535 tiles in one step");
@@ -457,7 +462,8 @@ TI_API int ti_attention_prefill_pair_sink_bf16(void* out, const void* q, const v
     p.out = (__nv_bfloat16*)out; p.tiles = tiles; p.block_table = block_table; p.max_blocks = max_blocks;
     p.hq = hq; p.hkv = hkv; p.page_size = page_size; p.num_pages = num_pages; p.window = window;
     p.scale_log2 = scale * 1.4426950408889634f; p.status = status;
-    p.has_sink = has_sink ? 1 : 0; p.sink_log2 = sink * 1.4426950408889634f; p.out_scale = out_scale;
+    p.has_sink = has_sink || head_sinks ? 1 : 0; p.sink_log2 = sink * 1.4426950408889634f; p.out_scale = out_scale;
+    p.head_sinks = head_sinks; p.gate = (const __nv_bfloat16*)gate; p.ld_gate = ld_gate; p.gate_off = gate_off;
     dim3 grid(hq, num_tiles);
     if (d == 128) {
         static bool once = false;
@@ -485,5 +491,5 @@ TI_API int ti_attention_prefill_pair_bf16(void* out, const void* q, const void* 
                                           int page_size, int num_pages, float scale, int window, int* status,
                                           cudaStream_t stream) {
     return ti_attention_prefill_pair_sink_bf16(out, q, kv_cache, tiles, num_tiles, num_tokens, block_table, max_blocks, hq, hkv,
-                                               d, page_size, num_pages, scale, window, 0, 0.f, 1.f, status, stream);
+                                               d, page_size, num_pages, scale, window, 0, 0.f, 1.f, nullptr, nullptr, 0, 0, status, stream);
 }

@@ -38,6 +38,9 @@ struct PrefillParams {
     float scale_log2;
     int has_sink;                    // the softmax denominator holds one more term 2^sink_log2 that has no value
     float sink_log2, out_scale;      // out_scale multiplies the output before its rounding
+    const float* head_sinks;         // float32 [query heads]: a sink's logit per head in place of sink_log2 (or null)
+    const __nv_bfloat16* gate;       // rows of ld_gate, first column gate_off: out *= sigmoid(gate[token][head]) (or null)
+    int ld_gate, gate_off;
     int* status;
 };
 
@@ -345,8 +348,8 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
                 sum_xch[half][r] = l_run;
                 asm volatile("bar.sync %0, 64;" ::"r"(1 + lane_group) : "memory");
                 const float l_all = l_run + sum_xch[half ^ 1][r];
-                const float l_fin = p.has_sink ? l_all + ex2(p.sink_log2 - m_run) : l_all;     // without a split of the keys
-                const float inv = l_fin > 0.f ? p.out_scale / l_fin : 0.f;
+                const float l_fin = p.has_sink ? l_all + ex2(ti_sink_log2(p, head) - m_run) : l_all;     // without a split of the keys
+                const float inv = l_fin > 0.f ? (r < nrows ? ti_head_out_scale(p, (size_t)(row0 + r), head) : 1.f) / l_fin : 0.f;
                 __nv_bfloat16* dst = p.out + ((size_t)(row0 + r) * p.hq + head) * D + half * DH;
                 const size_t part = (((size_t)blockIdx.y * p.splits + blockIdx.z) * p.hq + head) * QM + r;
                 if (p.splits > 1 && half == 0 && r < nrows)
@@ -414,8 +417,9 @@ __global__ void prefill_merge_kernel(const PrefillParams p) {
         l_all = l_all * keep + f * ml.y;
         m_run = m_new;
     }
-    if (p.has_sink) l_all += ex2(p.sink_log2 - m_run);
-    p.out[((size_t)(row0 + r) * p.hq + head) * D + d] = __float2bfloat16_rn(l_all > 0.f ? acc * p.out_scale / l_all : 0.f);
+    if (p.has_sink) l_all += ex2(ti_sink_log2(p, head) - m_run);
+    p.out[((size_t)(row0 + r) * p.hq + head) * D + d] =
+        __float2bfloat16_rn(l_all > 0.f ? acc * ti_head_out_scale(p, (size_t)(row0 + r), head) / l_all : 0.f);
 }
 
 }  // namespace
@@ -433,12 +437,14 @@ TI_API int ti_attention_prefill_tile_rows() { return QM; }
 TI_API long long ti_attention_prefill_scratch_floats(int num_tiles, int halves, int splits, int hq, int d) {
     return (long long)num_tiles * (halves ? 2 : 1) * splits * hq * QM * (d + 2);
 }
-// has_sink: exp(sink) joins every softmax denominator without a value; out_scale: a factor on the output.
+// has_sink: exp(sink) joins every softmax denominator without a value; out_scale: a factor on the output;
+// head_sinks, gate: a sink per query head, and a sigmoid gate per (token, query head) on the output (or null).
 TI_API int ti_attention_prefill_tc_sink_bf16(void* out, const void* q, const void* kv_cache, const int* tiles, int num_tiles,
                                              int num_tokens, const int* block_table, int max_blocks, int hq, int hkv, int d,
                                              int page_size, int num_pages, float scale, int window, int halves, int splits,
                                              int split_keys, float* scratch, long long scratch_floats, int has_sink, float sink,
-                                             float out_scale, int* status, cudaStream_t stream) {
+                                             float out_scale, const float* head_sinks, const void* gate, int ld_gate,
+                                             int gate_off, int* status, cudaStream_t stream) {
     TI_REQUIRE(splits >= 1 && splits <= 65535, "attention_prefill_tc: %d shares of the keys", splits);
     TI_REQUIRE(splits == 1 || (split_keys > 0 && split_keys % KT == 0 && scratch != nullptr &&
                                scratch_floats >= ti_attention_prefill_scratch_floats(num_tiles, halves, splits, hq, d)),
@@ -457,7 +463,8 @@ TI_API int ti_attention_prefill_tc_sink_bf16(void* out, const void* q, const voi
     p.out = (__nv_bfloat16*)out; p.tiles = tiles; p.block_table = block_table; p.max_blocks = max_blocks;
     p.hq = hq; p.hkv = hkv; p.page_size = page_size; p.num_pages = num_pages; p.window = window;
     p.scale_log2 = scale * 1.4426950408889634f; p.status = status; p.halves = halves ? 1 : 0;
-    p.has_sink = has_sink ? 1 : 0; p.sink_log2 = sink * 1.4426950408889634f; p.out_scale = out_scale;
+    p.has_sink = has_sink || head_sinks ? 1 : 0; p.sink_log2 = sink * 1.4426950408889634f; p.out_scale = out_scale;
+    p.head_sinks = head_sinks; p.gate = (const __nv_bfloat16*)gate; p.ld_gate = ld_gate; p.gate_off = gate_off;
     const int slots = halves ? 2 * num_tiles : num_tiles;
     p.splits = splits; p.split_keys = split_keys;
     p.part_o = scratch; p.part_ml = scratch ? scratch + (long long)slots * splits * hq * QM * d : nullptr;
@@ -495,5 +502,5 @@ TI_API int ti_attention_prefill_tc_bf16(void* out, const void* q, const void* kv
                                         cudaStream_t stream) {
     return ti_attention_prefill_tc_sink_bf16(out, q, kv_cache, tiles, num_tiles, num_tokens, block_table, max_blocks, hq, hkv, d,
                                              page_size, num_pages, scale, window, halves, splits, split_keys, scratch,
-                                             scratch_floats, 0, 0.f, 1.f, status, stream);
+                                             scratch_floats, 0, 0.f, 1.f, nullptr, nullptr, 0, 0, status, stream);
 }

@@ -110,3 +110,16 @@ __device__ __forceinline__ float block_max(float v, float* red) {
     __syncthreads();
     return r;
 }
+
+// A softmax sink and an output factor that may differ from head to head. P is an attention kernel's parameter block with
+// sink_log2 / head_sinks (float32 natural-log logits per query head, or null) and out_scale / gate (bfloat16 rows of
+// ld_gate elements, first column gate_off, one logit per (token, query head), or null: the output is also multiplied by
+// sigmoid(gate)).
+template <typename P> __device__ __forceinline__ float ti_sink_log2(const P& p, int head) {
+    return p.head_sinks ? p.head_sinks[head] * 1.4426950408889634f : p.sink_log2;
+}
+template <typename P> __device__ __forceinline__ float ti_head_out_scale(const P& p, size_t row, int head) {
+    if (!p.gate) return p.out_scale;
+    const float z = __bfloat162float(p.gate[row * p.ld_gate + p.gate_off + head]);
+    return p.out_scale / (1.f + expf(-z));
+}

@@ -375,6 +375,7 @@ __global__ void __launch_bounds__(AR_THREADS) attention_rows_kernel(
     T* __restrict__ out, const T* __restrict__ q, const T* __restrict__ cache, const int* __restrict__ positions,
     const int* __restrict__ token_seq, const int* __restrict__ block_table, int max_blocks, int hq, int hkv, int d, int dv,
     int page_size, int num_pages, int row, long long v_off, float scale, int window, int has_sink, float sink,
+    const float* __restrict__ head_sinks, const T* __restrict__ gate, int ld_gate, int gate_off,
     float out_scale, int* __restrict__ status) {
     __shared__ float qs[AR_MAX_D];
     __shared__ float p[AR_THREADS];
@@ -393,6 +394,11 @@ __global__ void __launch_bounds__(AR_THREADS) attention_rows_kernel(
     __syncthreads();
 
     float acc0 = 0.f, acc1 = 0.f;
+    if (head_sinks) { has_sink = 1; sink = head_sinks[h]; }            // a learned sink per query head
+    if (gate) {                                                          // a sigmoid gate per (token, query head)
+        const float z = to_f32(gate[(size_t)t * ld_gate + gate_off + h]);
+        out_scale *= 1.f / (1.f + expf(-z));
+    }
     float m = has_sink ? sink : -INFINITY, l = has_sink ? 1.f : 0.f;
     for (int tile0 = lo; tile0 <= pos; tile0 += AR_THREADS) {
         const int j = tile0 + tid;
@@ -441,10 +447,13 @@ __global__ void __launch_bounds__(AR_THREADS) attention_rows_kernel(
 }
 
 // planes 1: cache [pages][hkv][page_size][d + dv]; planes 2 (d == dv): [2][pages][hkv][page_size][d].
-// out: [T][hq * dv], multiplied by out_scale before its one rounding.
+// out: [T][hq * dv], multiplied by out_scale before its one rounding. head_sinks (float32 [hq], or null): a sink's
+// logit per query head in place of the one `sink`; gate (compute dtype, rows of ld_gate, first column gate_off, or
+// null): the output of (token, head) is also multiplied by sigmoid(gate[token][head]).
 TI_API int ti_attention_rows(void* out, const void* q, const void* cache, const int* positions, const int* token_seq,
                              const int* block_table, int max_blocks, int num_tokens, int hq, int hkv, int d, int dv,
                              int page_size, int num_pages, int planes, float scale, int window, int has_sink, float sink,
+                             const float* head_sinks, const void* gate, int ld_gate, int gate_off,
                              float out_scale, int* status, int dtype, cudaStream_t stream) {
     TI_REQUIRE(planes == 1 || (planes == 2 && d == dv), "attention_rows: two planes need keys and values of one size");
     const int row = planes == 2 ? d : d + dv;
@@ -458,11 +467,12 @@ TI_API int ti_attention_rows(void* out, const void* q, const void* cache, const 
     if (dtype == TI_F32)
         ti_launch(attention_rows_kernel<float>, grid, AR_THREADS, 0, stream, (float*)out, (const float*)q, (const float*)cache,
                   positions, token_seq, block_table, max_blocks, hq, hkv, d, dv, page_size, num_pages, row, v_off, scale, window,
-                  has_sink, sink, out_scale, status);
+                  has_sink, sink, head_sinks, (const float*)gate, ld_gate, gate_off, out_scale, status);
     else if (dtype == TI_BF16)
         ti_launch(attention_rows_kernel<__nv_bfloat16>, grid, AR_THREADS, 0, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)q,
                   (const __nv_bfloat16*)cache, positions, token_seq, block_table, max_blocks, hq, hkv, d, dv, page_size,
-                  num_pages, row, v_off, scale, window, has_sink, sink, out_scale, status);
+                  num_pages, row, v_off, scale, window, has_sink, sink, head_sinks, (const __nv_bfloat16*)gate, ld_gate, gate_off,
+                  out_scale, status);
     else TI_REQUIRE(false, "attention_rows: unknown dtype %d", dtype);
     TI_CHECK_LAUNCH("attention_rows");
     return 0;

@@ -1,7 +1,11 @@
 // A feed-forward made of many small experts, of which every token runs a few chosen by a router.
-//   route    : z = W_router x in float32 from the float32 residual row, s = softmax(z) over all experts, the `top`
-//              largest s (first index on ties), weights s_k / (sum of the chosen + weight_eps); also counts the tokens of
-//              every expert and gives each (token, choice) its rank among them
+//   route    : z = W_router x in float32 from the token's row (the float32 residual, or a sublayer's input in the
+//              compute dtype), s = softmax(z) over all experts, the `top` largest s + correction (a learned number per
+//              expert that only steers the choice; first index on ties), weights s_k / (sum of the chosen + weight_eps)
+//              or, without renormalisation, s_k itself; also counts the tokens of every expert and gives each
+//              (token, choice) its rank among them. The last experts of the router may be identity experts, whose
+//              output is the token's row itself: they have no weights, the plan gives them no tiles, and `combine`
+//              adds weight * row for them
 //   plan     : one block: where every expert's rows start in the sorted order, and the list of row tiles
 //              [expert, first row, rows] that the grouped product walks
 //   place    : slot of every (token, choice) in the sorted order and the token of every slot
@@ -9,6 +13,9 @@
 //              form gathers its rows from the tokens and applies max(v, 0)^2, the down form reads the sorted rows
 //   combine_norm_add : y = sum_k weight_k * down[slot_k] (+ the shared expert's output), in choice order, then the
 //              residual x32 += w * y * rsqrt(mean(y^2) + eps) and its copy in the compute dtype
+//   combine  : the same weighted sum alone, identity experts included, in the compute dtype
+//   clamped_glu : an expert's gated activation on the stored product [gate | up]: g = min(gate, limit),
+//              u = clamp(up, -limit, limit), g * sigmoid(alpha * g) * (u + 1)
 // A token's result depends on its own row alone: no capacity, nothing dropped, whatever else is in the batch.
 // Nothing here reads back to the host: grids are sized for the worst case and tiles beyond the plan's count return.
 #include "common.cuh"
@@ -22,19 +29,19 @@ constexpr int EX_MAX_TOP = 16;
 constexpr int EX_PER_LANE = 8;
 constexpr int EX_ROUTE_THREADS = 512;
 
-template <typename T>
+template <typename T, typename XT>
 __global__ void __launch_bounds__(EX_ROUTE_THREADS) moe_route_kernel(
     int* __restrict__ chosen, float* __restrict__ weight, int* __restrict__ rank, int* __restrict__ counts,
-    const float* __restrict__ x32, const T* __restrict__ w_router, int num_tokens, int hidden, int experts, int top,
-    float weight_eps) {
+    const XT* __restrict__ x32, const T* __restrict__ w_router, int num_tokens, int hidden, int experts, int top,
+    float weight_eps, const float* __restrict__ correction, int renorm) {
     __shared__ float logits[32 * EX_PER_LANE];
     ti_grid_launch_dependents();
     ti_grid_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x;
-    const float* x = x32 + (size_t)t * hidden;
+    const XT* x = x32 + (size_t)t * hidden;
     constexpr int VEC = 16 / sizeof(T);
-    const bool aligned = hidden % VEC == 0 && ((uintptr_t)w_router & 15) == 0 && ((uintptr_t)x32 & 15) == 0;
+    const bool aligned = sizeof(XT) == 4 && hidden % VEC == 0 && ((uintptr_t)w_router & 15) == 0 && ((uintptr_t)x32 & 15) == 0;
     for (int e = warp; e < experts; e += EX_ROUTE_THREADS / 32) {
         const T* w = w_router + (size_t)e * hidden;
         float dot = 0.f;
@@ -44,7 +51,7 @@ __global__ void __launch_bounds__(EX_ROUTE_THREADS) moe_route_kernel(
             for (int v = lane; v < hidden / VEC; v += 32) {
                 const uint4 q = w4[v];
                 const T* we = reinterpret_cast<const T*>(&q);
-                const float4* xp = reinterpret_cast<const float4*>(x + (size_t)v * VEC);
+                const float4* xp = reinterpret_cast<const float4*>(reinterpret_cast<const float*>(x) + (size_t)v * VEC);
 #pragma unroll
                 for (int i = 0; i < VEC / 4; ++i) {
                     const float4 f = xp[i];
@@ -55,7 +62,7 @@ __global__ void __launch_bounds__(EX_ROUTE_THREADS) moe_route_kernel(
                 }
             }
         } else {
-            for (int i = lane; i < hidden; i += 32) dot = fmaf(x[i], to_f32(w[i]), dot);
+            for (int i = lane; i < hidden; i += 32) dot = fmaf(to_f32(x[i]), to_f32(w[i]), dot);
         }
         dot = warp_sum(dot);
         if (lane == 0) logits[e] = dot;
@@ -80,43 +87,50 @@ __global__ void __launch_bounds__(EX_ROUTE_THREADS) moe_route_kernel(
     const float inv = 1.f / sum;
 #pragma unroll
     for (int k = 0; k < EX_PER_LANE; ++k) if (s[k] >= 0.f) s[k] *= inv;
+    // what the choice goes by: the score plus the expert's correction; -inf: no such expert, or taken already
+    float c[EX_PER_LANE];
+#pragma unroll
+    for (int k = 0; k < EX_PER_LANE; ++k)
+        c[k] = s[k] < 0.f ? -INFINITY : (correction ? s[k] + correction[k * 32 + lane] : s[k]);
     float best[EX_MAX_TOP];
     int who[EX_MAX_TOP];
     float total = 0.f;
-    for (int c = 0; c < top; ++c) {
-        float v = -1.f;
+    for (int ch = 0; ch < top; ++ch) {
+        float v = -INFINITY, sv = 0.f;
         int idx = 0x7fffffff;
 #pragma unroll
         for (int k = 0; k < EX_PER_LANE; ++k)
-            if (s[k] > v) { v = s[k]; idx = k * 32 + lane; }         // ascending index within a lane: the first wins
+            if (c[k] > v) { v = c[k]; sv = s[k]; idx = k * 32 + lane; }     // ascending index within a lane: the first wins
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) {
             const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+            const float os = __shfl_xor_sync(0xffffffffu, sv, o);
             const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
-            if (ov > v || (ov == v && oi < idx)) { v = ov; idx = oi; }
+            if (ov > v || (ov == v && oi < idx)) { v = ov; sv = os; idx = oi; }
         }
-        best[c] = v;
-        who[c] = idx;
-        total += v;
+        best[ch] = sv;
+        who[ch] = idx;
+        total += sv;
 #pragma unroll
         for (int k = 0; k < EX_PER_LANE; ++k)
-            if (idx == k * 32 + lane) s[k] = -1.f;
+            if (idx == k * 32 + lane) c[k] = -INFINITY;
     }
     if (lane == 0) {
-        const float norm = 1.f / (total + weight_eps);
-        for (int c = 0; c < top; ++c) {
-            chosen[(size_t)t * top + c] = who[c];
-            weight[(size_t)t * top + c] = best[c] * norm;
-            rank[(size_t)t * top + c] = atomicAdd(counts + who[c], 1);
+        const float norm = renorm ? 1.f / (total + weight_eps) : 1.f;
+        for (int ch = 0; ch < top; ++ch) {
+            chosen[(size_t)t * top + ch] = who[ch];
+            weight[(size_t)t * top + ch] = best[ch] * norm;
+            rank[(size_t)t * top + ch] = atomicAdd(counts + who[ch], 1);
         }
     }
 }
 
 // ------------------------------------------------------------------ plan
-// counts[e] -> starts[e] (exclusive sums, starts[experts] = all rows) and tiles [expert, first row, rows];
-// num_tiles[0] = how many. One block; experts and tiles are few.
+// counts[e] -> starts[e] (exclusive sums, starts[experts] = all rows) and tiles [expert, first row, rows] of the
+// first real_experts experts (the others have no weights to multiply by); num_tiles[0] = how many. One block;
+// experts and tiles are few.
 __global__ void moe_plan_kernel(int* __restrict__ starts, int* __restrict__ tiles, int* __restrict__ num_tiles,
-                                const int* __restrict__ counts, int experts, int tile_rows, int max_tiles) {
+                                const int* __restrict__ counts, int experts, int real_experts, int tile_rows, int max_tiles) {
     ti_grid_launch_dependents();
     ti_grid_wait();
     if (threadIdx.x != 0) return;
@@ -124,7 +138,7 @@ __global__ void moe_plan_kernel(int* __restrict__ starts, int* __restrict__ tile
     for (int e = 0; e < experts; ++e) {
         starts[e] = row;
         const int c = counts[e];
-        for (int r = 0; r < c && n < max_tiles; r += tile_rows) {
+        for (int r = 0; r < c && n < max_tiles && e < real_experts; r += tile_rows) {      // identity experts: rows, no tiles
             tiles[3 * n] = e;
             tiles[3 * n + 1] = row + r;
             tiles[3 * n + 2] = min(tile_rows, c - r);
@@ -147,26 +161,33 @@ __global__ void moe_place_kernel(int* __restrict__ slot_of, int* __restrict__ to
     token_of[slot] = i / top;
 }
 
-// counts (experts ints) must be zero on entry; the launcher clears them.
+// counts (experts ints) must be zero on entry; the launcher clears them. x_dtype: of the tokens' rows (float32, or
+// the compute dtype of a sublayer's input); correction: float32 [experts] or null; renorm: the weights are divided by
+// their sum; real_experts: how many of the router's outputs are experts with weights (the rest: identity experts).
 TI_API int ti_moe_route(int* chosen, float* weight, int* rank, int* counts, int* starts, int* tiles, int* num_tiles,
-                        int* slot_of, int* token_of, const float* x32, const void* w_router, int num_tokens, int hidden,
-                        int experts, int top, float weight_eps, int tile_rows, int max_tiles, int dtype, cudaStream_t stream) {
+                        int* slot_of, int* token_of, const void* x, const void* w_router, int num_tokens, int hidden,
+                        int experts, int top, float weight_eps, const float* correction, int renorm, int real_experts,
+                        int tile_rows, int max_tiles, int x_dtype, int dtype, cudaStream_t stream) {
     TI_REQUIRE(num_tokens >= 0 && hidden > 0 && experts > 0 && top > 0, "moe_route: bad sizes");
     TI_REQUIRE(top <= EX_MAX_TOP && top <= experts, "moe_route: top %d of %d experts (at most %d)", top, experts, EX_MAX_TOP);
     TI_REQUIRE(experts <= 32 * EX_PER_LANE, "moe_route: more than %d experts", 32 * EX_PER_LANE);
+    TI_REQUIRE(real_experts >= 0 && real_experts <= experts, "moe_route: %d of %d experts have weights", real_experts, experts);
+    TI_REQUIRE(x_dtype == TI_F32 || x_dtype == dtype, "moe_route: the rows are float32 or of the router's dtype");
     if (num_tokens == 0) return 0;
     cudaError_t e = cudaMemsetAsync(counts, 0, sizeof(int) * experts, stream);
     TI_REQUIRE(e == cudaSuccess, "moe_route: %s", cudaGetErrorString(e));
     const int blocks = num_tokens;
-    if (dtype == TI_F32)
-        ti_launch(moe_route_kernel<float>, blocks, EX_ROUTE_THREADS, 0, stream, chosen, weight, rank, counts, x32, (const float*)w_router,
-                  num_tokens, hidden, experts, top, weight_eps);
-    else if (dtype == TI_BF16)
-        ti_launch(moe_route_kernel<__nv_bfloat16>, blocks, EX_ROUTE_THREADS, 0, stream, chosen, weight, rank, counts, x32,
-                  (const __nv_bfloat16*)w_router, num_tokens, hidden, experts, top, weight_eps);
+    typedef __nv_bfloat16 B;
+#define EX_ROUTE(T, XT) ti_launch(moe_route_kernel<T, XT>, blocks, EX_ROUTE_THREADS, 0, stream, chosen, weight, rank, counts, \
+                                  (const XT*)x, (const T*)w_router, num_tokens, hidden, experts, top, weight_eps, correction, renorm)
+    if (dtype == TI_F32) EX_ROUTE(float, float);
+    else if (dtype == TI_BF16 && x_dtype == TI_F32) EX_ROUTE(B, float);
+    else if (dtype == TI_BF16) EX_ROUTE(B, B);
     else TI_REQUIRE(false, "moe_route: unknown dtype %d", dtype);
+#undef EX_ROUTE
     TI_CHECK_LAUNCH("moe_route");
-    ti_launch(moe_plan_kernel, 1, 32, 0, stream, starts, tiles, num_tiles, (const int*)counts, experts, tile_rows, max_tiles);
+    ti_launch(moe_plan_kernel, 1, 32, 0, stream, starts, tiles, num_tiles, (const int*)counts, experts, real_experts, tile_rows,
+              max_tiles);
     TI_CHECK_LAUNCH("moe_plan");
     const int n = num_tokens * top;
     ti_launch(moe_place_kernel, (n + 127) / 128, 128, 0, stream, slot_of, token_of, (const int*)chosen, (const int*)rank,
@@ -277,8 +298,8 @@ __global__ void __launch_bounds__(mt::THREADS) moe_gemm_mma_kernel(
 
 TI_API int ti_moe_tile_rows() { return EG_BM; }
 
-// up != 0: x [tokens, K] gathered through token_of, out [slots, N] in the compute dtype after max(v, 0)^2;
-// else x [slots, K], out [slots, N] float32. w [experts, N, K]. max_tiles: the grid's height.
+// up != 0: x [tokens, K] gathered through token_of, out [slots, N] in the compute dtype after max(v, 0)^2 (up == 1)
+// or as it is (up == 2: the activation is a kernel of its own); else x [slots, K], out [slots, N] float32. w [experts, N, K]. max_tiles: the grid's height.
 // 1 if row tiles of 64 are taken for these operands (the tensor-core form), else the plan must cut tiles of 32.
 TI_API int ti_moe_wide_tiles_ok(int K, int dtype) { return dtype == TI_BF16 && K % 8 == 0 ? 1 : 0; }
 
@@ -291,16 +312,18 @@ TI_API int ti_moe_gemm(void* out, const void* x, const void* w, const int* tiles
     dim3 grid((N + EG_BN - 1) / EG_BN, max_tiles);
     typedef __nv_bfloat16 B;
     if (dtype == TI_F32) {
-        if (up) ti_launch(moe_gemm_kernel<float, float, true, true>, grid, EG_THREADS, 0, stream, (float*)out, (const float*)x, (const float*)w, tiles, num_tiles, token_of, N, K);
+        if (up == 2) ti_launch(moe_gemm_kernel<float, float, true, false>, grid, EG_THREADS, 0, stream, (float*)out, (const float*)x, (const float*)w, tiles, num_tiles, token_of, N, K);
+        else if (up) ti_launch(moe_gemm_kernel<float, float, true, true>, grid, EG_THREADS, 0, stream, (float*)out, (const float*)x, (const float*)w, tiles, num_tiles, token_of, N, K);
         else ti_launch(moe_gemm_kernel<float, float, false, false>, grid, EG_THREADS, 0, stream, (float*)out, (const float*)x, (const float*)w, tiles, num_tiles, token_of, N, K);
     } else if (tensor_cores) {
         dim3 mgrid((N + mt::BN - 1) / mt::BN, max_tiles);
 #define EG_MMA(O, G, R, MI) ti_launch(moe_gemm_mma_kernel<O, G, R, MI>, mgrid, mt::THREADS, 0, stream, (O*)out, (const B*)x, (const B*)w, tiles, num_tiles, token_of, N, K)
-        if (tile_rows == 64) { if (up) EG_MMA(B, true, true, 4); else EG_MMA(float, false, false, 4); }
-        else { if (up) EG_MMA(B, true, true, 2); else EG_MMA(float, false, false, 2); }
+        if (tile_rows == 64) { if (up == 2) EG_MMA(B, true, false, 4); else if (up) EG_MMA(B, true, true, 4); else EG_MMA(float, false, false, 4); }
+        else { if (up == 2) EG_MMA(B, true, false, 2); else if (up) EG_MMA(B, true, true, 2); else EG_MMA(float, false, false, 2); }
 #undef EG_MMA
     } else if (dtype == TI_BF16) {
-        if (up) ti_launch(moe_gemm_kernel<B, B, true, true>, grid, EG_THREADS, 0, stream, (B*)out, (const B*)x, (const B*)w, tiles, num_tiles, token_of, N, K);
+        if (up == 2) ti_launch(moe_gemm_kernel<B, B, true, false>, grid, EG_THREADS, 0, stream, (B*)out, (const B*)x, (const B*)w, tiles, num_tiles, token_of, N, K);
+        else if (up) ti_launch(moe_gemm_kernel<B, B, true, true>, grid, EG_THREADS, 0, stream, (B*)out, (const B*)x, (const B*)w, tiles, num_tiles, token_of, N, K);
         else ti_launch(moe_gemm_kernel<B, float, false, false>, grid, EG_THREADS, 0, stream, (float*)out, (const B*)x, (const B*)w, tiles, num_tiles, token_of, N, K);
     } else TI_REQUIRE(false, "moe_gemm: unknown dtype %d", dtype);
     TI_CHECK_LAUNCH("moe_gemm");
@@ -388,5 +411,76 @@ TI_API int ti_moe_combine_norm_add(float* x32, void* copy, const float* down, co
                   (const __nv_bfloat16*)shared_out, slot_of, weight, norm_w, size, top, eps);
     else TI_REQUIRE(false, "moe_combine: unknown dtype %d", dtype);
     TI_CHECK_LAUNCH("moe_combine_norm_add");
+    return 0;
+}
+
+// ------------------------------------------------------------------ gated activation of an expert, combine alone
+// in [rows][2 * ff] = [gate | up] as the grouped product stored it; out [rows][ff].
+template <typename T>
+__global__ void moe_clamped_glu_kernel(T* __restrict__ out, const T* __restrict__ in, size_t rows, int ff, float limit, float alpha) {
+    ti_grid_launch_dependents();
+    ti_grid_wait();
+    const size_t n = rows * ff, stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
+        const size_t r = i / ff;
+        const int c = (int)(i % ff);
+        const float g = fminf(to_f32(in[r * 2 * ff + c]), limit);
+        const float u = fminf(fmaxf(to_f32(in[r * 2 * ff + ff + c]), -limit), limit);
+        out[i] = from_f32<T>(g / (1.f + expf(-alpha * g)) * (u + 1.f));
+    }
+}
+
+TI_API int ti_moe_clamped_glu(void* out, const void* in, long long rows, int ff, float limit, float alpha, int dtype,
+                              cudaStream_t stream) {
+    TI_REQUIRE(rows >= 0 && ff > 0, "moe_clamped_glu: bad sizes");
+    if (rows == 0) return 0;
+    const long long want = (rows * ff + 255) / 256;
+    const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
+    if (dtype == TI_F32) ti_launch(moe_clamped_glu_kernel<float>, blocks, 256, 0, stream, (float*)out, (const float*)in, (size_t)rows, ff, limit, alpha);
+    else if (dtype == TI_BF16) ti_launch(moe_clamped_glu_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)in, (size_t)rows, ff, limit, alpha);
+    else TI_REQUIRE(false, "moe_clamped_glu: unknown dtype %d", dtype);
+    TI_CHECK_LAUNCH("moe_clamped_glu");
+    return 0;
+}
+
+// out[t] = sum_c weight[t][c] * (chosen[t][c] < real_experts ? down[slot_of[t][c]] : x[t]), in choice order, float32
+// sums, one rounding. A block a token.
+template <typename T>
+__global__ void moe_combine_kernel(T* __restrict__ out, const float* __restrict__ down, const T* __restrict__ x,
+                                   const int* __restrict__ chosen, const int* __restrict__ slot_of,
+                                   const float* __restrict__ weight, int size, int top, int real_experts) {
+    __shared__ int slots[EX_MAX_TOP];
+    __shared__ float wts[EX_MAX_TOP];
+    ti_grid_launch_dependents();
+    ti_grid_wait();
+    const int t = blockIdx.x;
+    if (threadIdx.x < top) {
+        const size_t at = (size_t)t * top + threadIdx.x;
+        slots[threadIdx.x] = chosen[at] < real_experts ? slot_of[at] : -1;
+        wts[threadIdx.x] = weight[at];
+    }
+    __syncthreads();
+    const size_t base = (size_t)t * size;
+    for (int i = threadIdx.x; i < size; i += blockDim.x) {
+        float v = 0.f;
+        for (int c = 0; c < top; ++c)
+            v = fmaf(wts[c], slots[c] >= 0 ? down[(size_t)slots[c] * size + i] : to_f32(x[base + i]), v);
+        out[base + i] = from_f32<T>(v);
+    }
+}
+
+TI_API int ti_moe_combine(void* out, const float* down, const void* x, const int* chosen, const int* slot_of,
+                          const float* weight, int num_tokens, int size, int top, int real_experts, int dtype,
+                          cudaStream_t stream) {
+    TI_REQUIRE(num_tokens >= 0 && size > 0 && top > 0 && top <= EX_MAX_TOP, "moe_combine: bad sizes");
+    if (num_tokens == 0) return 0;
+    int threads = 32;
+    while (threads < 512 && threads * 4 < size) threads <<= 1;
+    if (dtype == TI_F32)
+        ti_launch(moe_combine_kernel<float>, num_tokens, threads, 0, stream, (float*)out, down, (const float*)x, chosen, slot_of, weight, size, top, real_experts);
+    else if (dtype == TI_BF16)
+        ti_launch(moe_combine_kernel<__nv_bfloat16>, num_tokens, threads, 0, stream, (__nv_bfloat16*)out, down, (const __nv_bfloat16*)x, chosen, slot_of, weight, size, top, real_experts);
+    else TI_REQUIRE(false, "moe_combine: unknown dtype %d", dtype);
+    TI_CHECK_LAUNCH("moe_combine");
     return 0;
 }

@@ -121,8 +121,10 @@ moe_gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_
                 if (!live || n0 + c >= p.N) continue;
                 const size_t at = (size_t)(row0 + r) * p.N + n0 + c;
                 if (p.up) {
+                    if (p.up == 1) {                          // up == 2: stored as it is, the activation is a kernel of its own
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) { v[i] = fmaxf(v[i], 0.f); v[i] *= v[i]; }
+                        for (int i = 0; i < 32; ++i) { v[i] = fmaxf(v[i], 0.f); v[i] *= v[i]; }
+                    }
                     __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.out) + at;
                     if (n0 + c + 32 <= p.N && (p.N & 7) == 0) {
 #pragma unroll
@@ -168,7 +170,7 @@ TI_API int ti_moe_gemm_tcgen05_ok(int slots, int experts, int N, int K) {
 TI_API int ti_moe_tcgen05_tile_rows() { return GT_BM; }
 
 // x: sorted rows [slots, K] bfloat16; w [experts, N, K] bfloat16; tiles/num_tiles: the plan with row tiles of 128.
-// up != 0: out [slots, N] bfloat16 after max(v, 0)^2; else out [slots, N] float32.
+// up == 1: out [slots, N] bfloat16 after max(v, 0)^2; up == 2: bfloat16 as it is; else out [slots, N] float32.
 TI_API int ti_moe_gemm_tcgen05(void* out, const void* x, const void* w, const int* tiles, const int* num_tiles, int slots,
                                int experts, int N, int K, int max_tiles, int up, int* status, cudaStream_t stream) {
     TI_REQUIRE(ti_moe_gemm_tcgen05_ok(slots, experts, N, K), "moe_gemm_tcgen05: operands [%d, %d] x [%d, %d, %d] are not taken", slots, K, experts, N, K);

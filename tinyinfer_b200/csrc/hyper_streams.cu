@@ -7,16 +7,17 @@
 // coefficients (if any). A block owns a token's row of every stream; the sums and the norm are float32, the
 // rounding of h to the compute dtype is the only one. With S = 1, c_in = c_mix = c_out = 1 this is the ordinary
 // pre-norm residual kept in float32.
-//   streams_embed : X[s][t] = table[id[t]] for every s
+//   streams_embed : X[s][t] = table[id[t]] * scale for every s
 //   streams_step  : as above; `rows` picks the tokens to work on (the rows whose logits are wanted)
 //   gelu, scale   : the feed-forward's activation on a stored tensor, and a constant factor on float32 logits
+//   soft_cap      : x <- cap * tanh(x / cap) on float32 logits
 #include "common.cuh"
 
 constexpr int HS_MAX_STREAMS = 8;
 
 template <typename T>
 __global__ void streams_embed_kernel(float* __restrict__ X, const T* __restrict__ table, const int* __restrict__ ids,
-                                     int num_tokens, int width, int vocab, int streams) {
+                                     int num_tokens, int width, int vocab, int streams, float scale) {
     ti_grid_launch_dependents();
     ti_grid_wait();
     const int t = blockIdx.x;
@@ -24,21 +25,21 @@ __global__ void streams_embed_kernel(float* __restrict__ X, const T* __restrict_
     const bool ok = id >= 0 && id < vocab;
     const T* src = table + (size_t)(ok ? id : 0) * width;
     for (int i = threadIdx.x; i < width; i += blockDim.x) {
-        const float v = ok ? to_f32(src[i]) : 0.f;
+        const float v = ok ? to_f32(src[i]) * scale : 0.f;
         for (int s = 0; s < streams; ++s) X[((size_t)s * num_tokens + t) * width + i] = v;
     }
 }
 
 TI_API int ti_streams_embed(float* X, const void* table, const int* ids, int num_tokens, int width, int vocab, int streams,
-                            int dtype, cudaStream_t stream) {
+                            float scale, int dtype, cudaStream_t stream) {
     TI_REQUIRE(num_tokens >= 0 && width > 0 && vocab > 0 && streams >= 1 && streams <= HS_MAX_STREAMS,
                "streams_embed: bad sizes (1..%d streams)", HS_MAX_STREAMS);
     if (num_tokens == 0) return 0;
     const int threads = width >= 1024 ? 256 : 128;
     if (dtype == TI_F32)
-        ti_launch(streams_embed_kernel<float>, num_tokens, threads, 0, stream, X, (const float*)table, ids, num_tokens, width, vocab, streams);
+        ti_launch(streams_embed_kernel<float>, num_tokens, threads, 0, stream, X, (const float*)table, ids, num_tokens, width, vocab, streams, scale);
     else if (dtype == TI_BF16)
-        ti_launch(streams_embed_kernel<__nv_bfloat16>, num_tokens, threads, 0, stream, X, (const __nv_bfloat16*)table, ids, num_tokens, width, vocab, streams);
+        ti_launch(streams_embed_kernel<__nv_bfloat16>, num_tokens, threads, 0, stream, X, (const __nv_bfloat16*)table, ids, num_tokens, width, vocab, streams, scale);
     else TI_REQUIRE(false, "streams_embed: unknown dtype %d", dtype);
     TI_CHECK_LAUNCH("streams_embed");
     return 0;
@@ -247,5 +248,22 @@ TI_API int ti_scale(float* x, long long n, float factor, cudaStream_t stream) {
     const long long want = (n + 255) / 256;
     ti_launch(scale_kernel, (int)(want < 148 * 16 ? want : 148 * 16), 256, 0, stream, x, (size_t)n, factor);
     TI_CHECK_LAUNCH("scale");
+    return 0;
+}
+
+__global__ void soft_cap_kernel(float* __restrict__ x, size_t n, float cap, float inv_cap) {
+    ti_grid_launch_dependents();
+    ti_grid_wait();
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) x[i] = cap * tanhf(x[i] * inv_cap);
+}
+
+// x <- cap * tanh(x / cap) in place (float32): logits that level off smoothly at +-cap.
+TI_API int ti_soft_cap(float* x, long long n, float cap, cudaStream_t stream) {
+    TI_REQUIRE(n >= 0 && cap > 0.f, "soft_cap: bad arguments");
+    if (n == 0) return 0;
+    const long long want = (n + 255) / 256;
+    ti_launch(soft_cap_kernel, (int)(want < 148 * 16 ? want : 148 * 16), 256, 0, stream, x, (size_t)n, cap, 1.f / cap);
+    TI_CHECK_LAUNCH("soft_cap");
     return 0;
 }

@@ -28,8 +28,8 @@
 // o_t += (q_t * D_t)^T S_start with D_t the product of the stretch's decays up to t: a plain product, no recurrence.
 // Four thirds of the arithmetic, as many times the blocks as there are stretches.
 //
-//   gated_group_norm : out = scale * w * n(y) * silu(gate)  or  scale * w * n(y * silu(gate)),  n: every group of
-//                      `group` features divided by its root mean square (float32), one rounding
+//   gated_group_norm : out = scale * w * n(y) * act(gate)  or  scale * w * n(y * act(gate)),  n: every group of
+//                      `group` features divided by its root mean square (float32), act silu or sigmoid, one rounding
 #include "common.cuh"
 
 enum { LS_GATE_RAW = 0, LS_GATE_SIGMOID_POW = 1, LS_GATE_STEP = 2 };
@@ -415,7 +415,7 @@ TI_API int ti_linear_scan(float* y, float* state, long long slot_stride, const v
 template <typename T>
 __global__ void gated_group_norm_kernel(T* __restrict__ out, const float* __restrict__ y, const T* __restrict__ gate,
                                         int ld_gate, int gate_off, const float* __restrict__ w, int w_len, int width,
-                                        int group, float eps, int gate_first, float out_scale) {
+                                        int group, float eps, int gate_first, float out_scale, int gate_sigmoid) {
     __shared__ float red[33];
     ti_grid_launch_dependents();
     ti_grid_wait();
@@ -427,7 +427,7 @@ __global__ void gated_group_norm_kernel(T* __restrict__ out, const float* __rest
         float v = yrow[i];
         if (gate_first && grow) {
             const float z = to_f32(grow[i]);
-            v *= z / (1.f + expf(-z));
+            v *= (gate_sigmoid ? 1.f : z) / (1.f + expf(-z));
         }
         ss += v * v;
     }
@@ -438,7 +438,7 @@ __global__ void gated_group_norm_kernel(T* __restrict__ out, const float* __rest
         float gz = 1.f;
         if (grow) {
             const float z = to_f32(grow[i]);
-            gz = z / (1.f + expf(-z));
+            gz = (gate_sigmoid ? 1.f : z) / (1.f + expf(-z));
         }
         if (gate_first) v *= gz;
         v = v * inv * w[(g0 + i) % w_len];
@@ -454,7 +454,7 @@ template <typename T>
 __global__ void gated_group_norm_warp_kernel(T* __restrict__ out, const float* __restrict__ y, const T* __restrict__ gate,
                                              int ld_gate, int gate_off, const float* __restrict__ w, int w_len, int width,
                                              int group, float eps, int gate_first, float out_scale, long long num_groups,
-                                             int wide_rows) {
+                                             int wide_rows, int gate_sigmoid) {
     constexpr int TRIPS = 4;                             // 4 trips x 32 lanes x 4 features = 512
     ti_grid_launch_dependents();
     ti_grid_wait();
@@ -476,7 +476,7 @@ __global__ void gated_group_norm_warp_kernel(T* __restrict__ out, const float* _
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const float z = grow ? to_f32(grow[i + e]) : 0.f;
-                gz[k][e] = grow ? z / (1.f + expf(-z)) : 1.f;
+                gz[k][e] = grow ? (gate_sigmoid ? 1.f : z) / (1.f + expf(-z)) : 1.f;
                 if (gate_first) v[k][e] *= gz[k][e];
                 ss += v[k][e] * v[k][e];
             }
@@ -514,7 +514,7 @@ __global__ void gated_group_norm_warp_kernel(T* __restrict__ out, const float* _
 
 TI_API int ti_gated_group_norm(void* out, const float* y, const void* gate, int ld_gate, int gate_off, const float* w,
                                int w_len, int num_tokens, int width, int group, float eps, int gate_first, float out_scale,
-                               int dtype, cudaStream_t stream) {
+                               int gate_sigmoid, int dtype, cudaStream_t stream) {
     TI_REQUIRE(num_tokens >= 0 && width > 0 && group > 0 && width % group == 0 && w_len > 0, "gated_group_norm: bad sizes");
     TI_REQUIRE(width / group <= 65535, "gated_group_norm: too many groups");
     if (num_tokens == 0) return 0;
@@ -524,11 +524,11 @@ TI_API int ti_gated_group_norm(void* out, const float* y, const void* gate, int 
         const int wide_rows = (uintptr_t)out % 16 == 0;          // width and group are multiples of four: rows of out start on 8 or 16 bytes
         if (dtype == TI_F32)
             ti_launch(gated_group_norm_warp_kernel<float>, blocks, 256, 0, stream, (float*)out, y, (const float*)gate, ld_gate,
-                      gate_off, w, w_len, width, group, eps, gate_first, out_scale, num_groups, wide_rows);
+                      gate_off, w, w_len, width, group, eps, gate_first, out_scale, num_groups, wide_rows, gate_sigmoid);
         else if (dtype == TI_BF16)
             ti_launch(gated_group_norm_warp_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (__nv_bfloat16*)out, y,
                       (const __nv_bfloat16*)gate, ld_gate, gate_off, w, w_len, width, group, eps, gate_first, out_scale, num_groups,
-                      wide_rows);
+                      wide_rows, gate_sigmoid);
         else TI_REQUIRE(false, "gated_group_norm: unknown dtype %d", dtype);
         TI_CHECK_LAUNCH("gated_group_norm");
         return 0;
@@ -538,10 +538,10 @@ TI_API int ti_gated_group_norm(void* out, const float* y, const void* gate, int 
     dim3 grid(num_tokens, width / group);
     if (dtype == TI_F32)
         ti_launch(gated_group_norm_kernel<float>, grid, threads, 0, stream, (float*)out, y, (const float*)gate, ld_gate, gate_off,
-                  w, w_len, width, group, eps, gate_first, out_scale);
+                  w, w_len, width, group, eps, gate_first, out_scale, gate_sigmoid);
     else if (dtype == TI_BF16)
         ti_launch(gated_group_norm_kernel<__nv_bfloat16>, grid, threads, 0, stream, (__nv_bfloat16*)out, y,
-                  (const __nv_bfloat16*)gate, ld_gate, gate_off, w, w_len, width, group, eps, gate_first, out_scale);
+                  (const __nv_bfloat16*)gate, ld_gate, gate_off, w, w_len, width, group, eps, gate_first, out_scale, gate_sigmoid);
     else TI_REQUIRE(false, "gated_group_norm: unknown dtype %d", dtype);
     TI_CHECK_LAUNCH("gated_group_norm");
     return 0;

@@ -70,8 +70,12 @@ _SIGNATURES = {
                            c_int, c_int, c_int, c_int, c_void_p],
         "ti_gated_scan": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p,
                           c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
+    },
+    # routed experts
+    "experts": {
         "ti_moe_route": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                         c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p],
+                         c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                         c_void_p],
         "ti_moe_tile_rows": [],
         "ti_moe_gemm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                         c_void_p],
@@ -79,11 +83,21 @@ _SIGNATURES = {
         "ti_moe_gather": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
         "ti_moe_combine_norm_add": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                     c_int, c_float, c_int, c_void_p],
+        "ti_moe_clamped_glu": [c_void_p, c_void_p, c_ll, c_int, c_float, c_float, c_int, c_void_p],
+        "ti_moe_combine": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                           c_void_p],
     },
     # parts of designs with several residual streams, short convolutions, attention over [key | value] rows and
     # linear attention with a matrix state
     "hybrid": {
-        "ti_streams_embed": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
+        "ti_streams_embed": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
+        "ti_soft_cap": [c_void_p, c_ll, c_float, c_void_p],
+        "ti_head_rotation": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_float, c_void_p,
+                             c_void_p, c_int, c_int, c_int, c_float, c_float, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                             c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p],
+        "ti_delta_scan": [c_void_p, c_void_p, c_ll, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int,
+                          c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_float, c_float, c_void_p,
+                          c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
         "ti_streams_step": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int,
                             c_int, c_int, c_int, c_int, c_int, c_void_p],
         "ti_gelu": [c_void_p, c_void_p, c_ll, c_int, c_int, c_void_p],
@@ -96,13 +110,14 @@ _SIGNATURES = {
                                c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                c_int, c_int, c_void_p, c_int, c_void_p],
         "ti_attention_rows": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                              c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_float, c_float, c_void_p, c_int, c_void_p],
+                              c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_float, c_void_p, c_void_p, c_int, c_int,
+                              c_float, c_void_p, c_int, c_void_p],
         "ti_linear_scan": [c_void_p, c_void_p, c_ll, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int,
                            c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p, c_float, c_void_p,
                            c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_ll, c_void_p, c_int, c_void_p],
         "ti_linear_scan_scratch_floats": [c_int, c_int, c_int, c_int, c_int, c_int],
         "ti_gated_group_norm": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_float,
-                                c_int, c_float, c_int, c_void_p],
+                                c_int, c_float, c_int, c_int, c_void_p],
     },
 }
 _SIGNATURES["sm100"] = {
@@ -132,13 +147,15 @@ _SIGNATURES["sm100"]["ti_attention_decode_bf16"] = [
     c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p]
 _SIGNATURES["sm100"]["ti_attention_decode_sink_bf16"] = [
     c_void_p, c_void_p, c_void_p, c_void_p, c_ll, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
-    c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_float, c_float, c_void_p, c_void_p]
+    c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_float, c_float, c_void_p, c_void_p, c_int, c_int,
+    c_void_p, c_void_p]
 _SIGNATURES["sm100"]["ti_attention_prefill_pair_sink_bf16"] = [
     c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
-    c_float, c_int, c_int, c_float, c_float, c_void_p, c_void_p]
+    c_float, c_int, c_int, c_float, c_float, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]
 _SIGNATURES["sm100"]["ti_attention_prefill_tc_sink_bf16"] = [
     c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
-    c_float, c_int, c_int, c_int, c_int, c_void_p, c_ll, c_int, c_float, c_float, c_void_p, c_void_p]
+    c_float, c_int, c_int, c_int, c_int, c_void_p, c_ll, c_int, c_float, c_float, c_void_p, c_void_p, c_int, c_int,
+    c_void_p, c_void_p]
 _SIGNATURES["sm100"]["ti_attention_decode_scratch_floats"] = [c_int, c_int, c_int, c_int, c_int, c_int]
 _SIGNATURES["sm100"]["ti_attention_prefill_pair_bf16"] = [
     c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
@@ -619,11 +636,14 @@ def paged_attention(q: torch.Tensor, kv_cache: torch.Tensor, *, positions: torch
                     token_seq: torch.Tensor, block_table: torch.Tensor, scale: float,
                     window: Optional[int] = None, step=None,
                     status: Optional[torch.Tensor] = None, sink: Optional[float] = None,
-                    out_scale: float = 1.0) -> torch.Tensor:
+                    out_scale: float = 1.0, head_sinks: Optional[torch.Tensor] = None,
+                    gate: Optional[torch.Tensor] = None, gate_offset: int = 0) -> torch.Tensor:
     """Causal attention of q [T, Hq, D] over the pages of each token's own request.
     Token t sees keys max(0, pos - window + 1) .. pos of request ``token_seq[t]``.
     ``sink``: a logit whose exponential joins every softmax denominator without a value (0.0 adds one to the sum
-    of exp(score)); ``out_scale``: a factor on the output before its rounding.
+    of exp(score)); ``head_sinks`` float32 [Hq]: such a logit per query head instead; ``gate`` [T, cols] of q's dtype:
+    the output of (token, head) is multiplied by sigmoid(gate[token, gate_offset + head]); ``out_scale``: a factor on
+    the output before its rounding.
     Returns [T, Hq * D]. ``step`` (the StepContext of the batch) carries the split of the batch
     into decoded tokens and prompt portions; without it the split is derived here (a device read)."""
     _check(q, "q", None, 3)
@@ -639,12 +659,15 @@ def paged_attention(q: torch.Tensor, kv_cache: torch.Tensor, *, positions: torch
     if t == 0:
         return out
     has_sink, sink_v = int(sink is not None), float(sink or 0.0)
+    _check_head_extras(q, head_sinks, gate, gate_offset)
+    extras = (_ptr(head_sinks), _ptr(gate), gate.shape[1] if gate is not None else 0, int(gate_offset))
     if not attention_tensor_cores_ok(q, kv_cache):
         if q.dtype == torch.bfloat16:
             _warn_generic_attention(hq, hkv, d, page_size)
-        if has_sink or out_scale != 1.0:
+        if has_sink or out_scale != 1.0 or head_sinks is not None or gate is not None:
             return attention_rows(q, kv_cache, v_dim=d, positions=positions, token_seq=token_seq, block_table=block_table,
-                                  scale=scale, sink=sink, window=window, out_scale=out_scale, status=status)
+                                  scale=scale, sink=sink, window=window, out_scale=out_scale, status=status,
+                                  head_sinks=head_sinks, gate=gate, gate_offset=gate_offset)
         _run("core", "ti_attention_generic", out.data_ptr(), q.data_ptr(), kv_cache.data_ptr(),
              positions.data_ptr(), token_seq.data_ptr(), block_table.data_ptr(), block_table.shape[1],
              t, hq, hkv, d, page_size, num_pages, float(scale), int(window or 0), _ptr(status),
@@ -680,8 +703,8 @@ def paged_attention(q: torch.Tensor, kv_cache: torch.Tensor, *, positions: torch
         _run("sm100", "ti_attention_decode_sink_bf16", out.data_ptr(), q.data_ptr(), kv_cache.data_ptr(),
              scratch.data_ptr(), scratch.numel(), decode_rows.data_ptr(), num_decode, positions.data_ptr(),
              token_seq.data_ptr(), block_table.data_ptr(), block_table.shape[1], hq, hkv, d, page_size,
-             num_pages, float(scale), int(window or 0), int(max_context), has_sink, sink_v, float(out_scale), kstatus,
-             _stream())
+             num_pages, float(scale), int(window or 0), int(max_context), has_sink, sink_v, float(out_scale), *extras,
+             kstatus, _stream())
     def one_tile_kernel(first: int, count: int, halves: int) -> None:
         # Few query tiles behind a long prefix: the keys are shared out over CTAs too (at least 1,024 to a CTA),
         # so that most SMs have a CTA; their partial results meet in a merge kernel.
@@ -697,12 +720,12 @@ def paged_attention(q: torch.Tensor, kv_cache: torch.Tensor, *, positions: torch
         _run("sm100", "ti_attention_prefill_tc_sink_bf16", out.data_ptr(), q.data_ptr(), kv_cache.data_ptr(),
              tiles.data_ptr() + 16 * first, count, t, block_table.data_ptr(), block_table.shape[1], hq, hkv, d, page_size,
              num_pages, float(scale), int(window or 0), halves, splits, split_keys, scratch_ptr, scratch_floats, has_sink,
-             sink_v, float(out_scale), kstatus, _stream())
+             sink_v, float(out_scale), *extras, kstatus, _stream())
 
     if num_pairs * hq >= PAIR_MIN_CTAS:             # two query tiles a CTA
         _run("sm100", "ti_attention_prefill_pair_sink_bf16", out.data_ptr(), q.data_ptr(), kv_cache.data_ptr(),
              tiles.data_ptr(), num_pairs, t, block_table.data_ptr(), block_table.shape[1], hq, hkv, d, page_size,
-             num_pages, float(scale), int(window or 0), has_sink, sink_v, float(out_scale), kstatus, _stream())
+             num_pages, float(scale), int(window or 0), has_sink, sink_v, float(out_scale), *extras, kstatus, _stream())
     elif num_pairs:                                 # too few of them to fill the machine: one query tile a CTA
         one_tile_kernel(0, num_pairs, 1)
     if num_tiles > num_pairs:                       # ends of portions of at most 128 rows
@@ -977,20 +1000,31 @@ class ExpertRouting:
 
 
 def route_experts(x32: torch.Tensor, w_router: torch.Tensor, top: int, weight_eps: float,
-                  wide_tiles: bool = False, tile_rows: int = 0) -> ExpertRouting:
-    """Router of a mixture of experts: float32 logits from the float32 rows ``x32`` [T, H] and ``w_router`` [E, H],
-    softmax over all experts, the ``top`` largest (first index on ties), weights = their scores over their sum
-    (+ ``weight_eps``). ``wide_tiles``: the row tiles of the plan hold 64 rows instead of 32 (for steps that bring
+                  wide_tiles: bool = False, tile_rows: int = 0, *, correction: Optional[torch.Tensor] = None,
+                  renormalize: bool = True, real_experts: Optional[int] = None) -> ExpertRouting:
+    """Router of a mixture of experts: float32 logits from the rows ``x32`` [T, H] (float32, or the router's dtype)
+    and ``w_router`` [E, H], softmax over all experts, the ``top`` largest (first index on ties), weights = their
+    scores over their sum (+ ``weight_eps``). ``correction`` float32 [E]: the choice goes by score + correction, the
+    weights stay the plain scores; ``renormalize`` False: the weights are the scores themselves; ``real_experts``:
+    only the first so many router outputs are experts with weights, the rest stand for identity experts (rows, but
+    no tiles in the plan). ``wide_tiles``: the row tiles of the plan hold 64 rows instead of 32 (for steps that bring
     an expert many rows; only the tensor-core grouped product takes them, see ``expert_tiles_may_be_wide``);
     ``tile_rows``: any other height the caller has settled with the grouped product (``expert_tile_rows``)."""
-    _check(x32, "x32", torch.float32, 2)
+    _check(x32, "x32", None, 2)
     _check(w_router, "w_router", None, 2)
+    if x32.dtype not in (torch.float32, w_router.dtype):
+        raise KernelError("route_experts: the rows are float32 or of the router's dtype")
     t, hidden = x32.shape
     experts = w_router.shape[0]
     if w_router.shape[1] != hidden:
         raise KernelError("route_experts: the router's rows do not match the stream's")
+    if correction is not None:
+        _check(correction, "correction", torch.float32, 1)
+        if correction.shape[0] != experts:
+            raise KernelError("route_experts: one correction per router output")
+    real = experts if real_experts is None else int(real_experts)
     dev = x32.device
-    tile_rows = tile_rows or (64 if wide_tiles else int(_fn("latent", "ti_moe_tile_rows")()))
+    tile_rows = tile_rows or (64 if wide_tiles else int(_fn("experts", "ti_moe_tile_rows")()))
     max_tiles = (t * top + tile_rows - 1) // tile_rows + experts
     ints = torch.empty(t * top * 4 + experts + (experts + 1) + 3 * max_tiles + 1, dtype=torch.int32, device=dev)
     n = t * top
@@ -1000,10 +1034,10 @@ def route_experts(x32: torch.Tensor, w_router: torch.Tensor, top: int, weight_ep
     o += 2 * experts + 1
     tiles, num_tiles = ints[o:o + 3 * max_tiles], ints[o + 3 * max_tiles:o + 3 * max_tiles + 1]
     weight = torch.empty((t, top), dtype=torch.float32, device=dev)
-    _run("latent", "ti_moe_route", chosen.data_ptr(), weight.data_ptr(), rank.data_ptr(), counts.data_ptr(),
+    _run("experts", "ti_moe_route", chosen.data_ptr(), weight.data_ptr(), rank.data_ptr(), counts.data_ptr(),
          starts.data_ptr(), tiles.data_ptr(), num_tiles.data_ptr(), slot_of.data_ptr(), token_of.data_ptr(),
-         x32.data_ptr(), w_router.data_ptr(), t, hidden, experts, top, float(weight_eps), tile_rows, max_tiles,
-         _dtype_code(w_router), _stream())
+         x32.data_ptr(), w_router.data_ptr(), t, hidden, experts, top, float(weight_eps), _ptr(correction),
+         int(renormalize), real, tile_rows, max_tiles, _dtype_code(x32), _dtype_code(w_router), _stream())
     return ExpertRouting(chosen.view(t, top), weight, slot_of.view(t, top), token_of, tiles.view(max_tiles, 3),
                          num_tiles, max_tiles, counts, tile_rows)
 
@@ -1011,7 +1045,7 @@ def route_experts(x32: torch.Tensor, w_router: torch.Tensor, top: int, weight_ep
 def expert_tiles_may_be_wide(x: torch.Tensor, *inner_sizes: int) -> bool:
     """True if the grouped products of ``x`` [T, K] (and of rows of the given other sizes) run on the tensor cores,
     which alone take row tiles of 64."""
-    return all(int(_fn("latent", "ti_moe_wide_tiles_ok")(k, _dtype_code(x))) for k in (x.shape[1],) + inner_sizes)
+    return all(int(_fn("experts", "ti_moe_wide_tiles_ok")(k, _dtype_code(x))) for k in (x.shape[1],) + inner_sizes)
 
 
 EXPERT_TCGEN05_MIN_ROWS = 96     # rows an expert gets on average from which the tcgen05 grouped product is used
@@ -1027,12 +1061,13 @@ def expert_tile_rows(x: torch.Tensor, num_experts: int, top: int, *inner_sizes: 
             return int(_fn("sm100", "ti_moe_tcgen05_tile_rows")())
     if t * top >= 48 * num_experts and expert_tiles_may_be_wide(x, *inner_sizes):
         return 64
-    return int(_fn("latent", "ti_moe_tile_rows")())
+    return int(_fn("experts", "ti_moe_tile_rows")())
 
 
-def expert_linear(x: torch.Tensor, w: torch.Tensor, routing: ExpertRouting, *, up: bool) -> torch.Tensor:
+def expert_linear(x: torch.Tensor, w: torch.Tensor, routing: ExpertRouting, *, up: bool, activation: bool = True) -> torch.Tensor:
     """Grouped product over the routing's row tiles with ``w`` [E, N, K]. ``up``: ``x`` [T, K] are the step's
-    tokens, gathered per expert; the result [T * top, N] (sorted rows) has passed max(v, 0)^2. Otherwise ``x``
+    tokens, gathered per expert; the result [T * top, N] (sorted rows) has passed max(v, 0)^2 (``activation``
+    False: it is stored as it is, for an activation that is a kernel of its own). Otherwise ``x``
     are sorted rows [T * top, K] and the result is float32 [T * top, N]."""
     _check(x, "x", None, 2)
     _check(w, "w", x.dtype, 3)
@@ -1041,18 +1076,19 @@ def expert_linear(x: torch.Tensor, w: torch.Tensor, routing: ExpertRouting, *, u
         raise KernelError("expert_linear: x and w do not match")
     slots = routing.token_of.shape[0]
     out = torch.empty((slots, n), dtype=x.dtype if up else torch.float32, device=x.device)
+    form = (1 if activation else 2) if up else 0
     if routing.tile_rows == 128:                 # tcgen05: tiled operand copies want the rows in expert order
         rows = x
         if up:
             rows = torch.empty((slots, k), dtype=x.dtype, device=x.device)
-            _run("latent", "ti_moe_gather", rows.data_ptr(), x.data_ptr(), routing.token_of.data_ptr(), slots, k,
+            _run("experts", "ti_moe_gather", rows.data_ptr(), x.data_ptr(), routing.token_of.data_ptr(), slots, k,
                  _dtype_code(x), _stream())
         _run("sm100", "ti_moe_gemm_tcgen05", out.data_ptr(), rows.data_ptr(), w.data_ptr(), routing.tiles.data_ptr(),
-             routing.num_tiles.data_ptr(), slots, w.shape[0], n, k, routing.max_tiles, int(up),
+             routing.num_tiles.data_ptr(), slots, w.shape[0], n, k, routing.max_tiles, form,
              kernel_status(x.device).data_ptr(), _stream())
         return out
-    _run("latent", "ti_moe_gemm", out.data_ptr(), x.data_ptr(), w.data_ptr(), routing.tiles.data_ptr(),
-         routing.num_tiles.data_ptr(), routing.token_of.data_ptr(), n, k, routing.max_tiles, routing.tile_rows, int(up),
+    _run("experts", "ti_moe_gemm", out.data_ptr(), x.data_ptr(), w.data_ptr(), routing.tiles.data_ptr(),
+         routing.num_tiles.data_ptr(), routing.token_of.data_ptr(), n, k, routing.max_tiles, routing.tile_rows, form,
          _dtype_code(x), _stream())
     return out
 
@@ -1068,21 +1104,51 @@ def experts_combine_norm_add(x32: torch.Tensor, down: torch.Tensor, shared_out: 
         _check(shared_out, "shared_out", copy_dtype, 2)
     t, size = x32.shape
     copy = None if copy_dtype == torch.float32 else torch.empty((t, size), dtype=copy_dtype, device=x32.device)
-    _run("latent", "ti_moe_combine_norm_add", x32.data_ptr(), _ptr(copy), down.data_ptr(), _ptr(shared_out),
+    _run("experts", "ti_moe_combine_norm_add", x32.data_ptr(), _ptr(copy), down.data_ptr(), _ptr(shared_out),
          routing.slot_of.data_ptr(), routing.weight.data_ptr(), norm_weight.data_ptr(), t, size,
          routing.chosen.shape[1], float(eps), 0 if copy is None else _dtype_code(copy), _stream())
     return x32, (x32 if copy is None else copy)
 
 
 # ---------------------------------------------------------------------- several residual streams
-def streams_embed(token_ids: torch.Tensor, table: torch.Tensor, streams: int) -> torch.Tensor:
-    """float32 [streams, T, width]: every stream starts as the rows ``table[token_ids]``."""
+def clamped_glu(gate_up: torch.Tensor, limit: float, alpha: float) -> torch.Tensor:
+    """The gated activation of an expert on its stored product ``gate_up`` [rows, 2 F] = [gate | up]:
+    g = min(gate, limit), u = clamp(up, -limit, limit), out = g * sigmoid(alpha * g) * (u + 1), [rows, F]; float32
+    arithmetic, one rounding."""
+    _check(gate_up, "gate_up", None, 2)
+    rows, two_f = gate_up.shape
+    if two_f % 2:
+        raise KernelError("clamped_glu: a row holds a gate half and an up half")
+    out = torch.empty((rows, two_f // 2), dtype=gate_up.dtype, device=gate_up.device)
+    _run("experts", "ti_moe_clamped_glu", out.data_ptr(), gate_up.data_ptr(), rows, two_f // 2, float(limit), float(alpha),
+         _dtype_code(gate_up), _stream())
+    return out
+
+
+def experts_combine(down: torch.Tensor, x: torch.Tensor, routing: ExpertRouting, real_experts: int) -> torch.Tensor:
+    """out[t] = sum_c weight[t, c] * (down[slot_of[t, c]] if chosen[t, c] < real_experts else x[t]) in choice order:
+    the weighted sum of the chosen experts' outputs (float32 sorted rows ``down``), an identity expert's output being
+    the token's own row of ``x`` [T, H]. Float32 sums, one rounding to x's dtype."""
+    _check(down, "down", torch.float32, 2)
+    _check(x, "x", None, 2)
+    t, size = x.shape
+    if down.shape[1] != size or routing.chosen.shape[0] != t:
+        raise KernelError("experts_combine: the rows do not fit the routing")
+    out = torch.empty_like(x)
+    _run("experts", "ti_moe_combine", out.data_ptr(), down.data_ptr(), x.data_ptr(), routing.chosen.data_ptr(),
+         routing.slot_of.data_ptr(), routing.weight.data_ptr(), t, size, routing.chosen.shape[1], int(real_experts),
+         _dtype_code(x), _stream())
+    return out
+
+
+def streams_embed(token_ids: torch.Tensor, table: torch.Tensor, streams: int, scale: float = 1.0) -> torch.Tensor:
+    """float32 [streams, T, width]: every stream starts as the rows ``table[token_ids]`` times ``scale``."""
     _check(token_ids, "token_ids", torch.int32, 1)
     _check(table, "table", None, 2)
     t, width = token_ids.shape[0], table.shape[1]
     out = torch.empty((streams, t, width), dtype=torch.float32, device=table.device)
     _run("hybrid", "ti_streams_embed", out.data_ptr(), table.data_ptr(), token_ids.data_ptr(), t, width, table.shape[0],
-         streams, _dtype_code(table), _stream())
+         streams, float(scale), _dtype_code(table), _stream())
     return out
 
 
@@ -1138,6 +1204,15 @@ def scale_(x: torch.Tensor, factor: float) -> torch.Tensor:
     _check(x, "x", torch.float32)
     if factor != 1.0:
         _run("hybrid", "ti_scale", x.data_ptr(), x.numel(), float(factor), _stream())
+    return x
+
+
+def soft_cap_(x: torch.Tensor, cap: float) -> torch.Tensor:
+    """x <- cap * tanh(x / cap) in place (float32)."""
+    _check(x, "x", torch.float32)
+    if not cap > 0:
+        raise KernelError("soft_cap_: the cap must be positive")
+    _run("hybrid", "ti_soft_cap", x.data_ptr(), x.numel(), float(cap), _stream())
     return x
 
 
@@ -1239,13 +1314,28 @@ def conv_qkv_append(qkv: torch.Tensor, *, num_heads: int, num_kv_heads: int, hea
     return q
 
 
+def _check_head_extras(q, head_sinks, gate, gate_offset) -> None:
+    t, hq, _ = q.shape
+    if head_sinks is not None:
+        _check(head_sinks, "head_sinks", torch.float32, 1)
+        if head_sinks.shape[0] != hq:
+            raise KernelError("attention: one sink per query head")
+    if gate is not None:
+        _check(gate, "gate", q.dtype, 2)
+        if gate.shape[0] != t or gate_offset < 0 or gate_offset + hq > gate.shape[1]:
+            raise KernelError("attention: the gate holds one column per query head for every token")
+
+
 def attention_rows(q: torch.Tensor, cache: torch.Tensor, *, v_dim: int, positions: torch.Tensor, token_seq: torch.Tensor,
                    block_table: torch.Tensor, scale: float, sink: Optional[float] = None, window: Optional[int] = None,
-                   out_scale: float = 1.0, step=None, status: Optional[torch.Tensor] = None) -> torch.Tensor:
+                   out_scale: float = 1.0, step=None, status: Optional[torch.Tensor] = None,
+                   head_sinks: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None,
+                   gate_offset: int = 0) -> torch.Tensor:
     """Causal attention of q [T, Hq, d] over pages whose rows are [k (d) | v (dv)] (``cache``
     [1, pages, Hkv, page, d + dv]; or planes [2, pages, Hkv, page, d] where d == dv), float32 arithmetic, any sizes. ``sink``: a logit whose exponential joins every softmax denominator without a
-    value (0.0: one is added to the sum of exp(score)). Returns [T, Hq * dv], multiplied by ``out_scale`` before
-    its rounding."""
+    value (0.0: one is added to the sum of exp(score)); ``head_sinks`` float32 [Hq]: such a logit per query head
+    instead. ``gate`` [T, cols] of q's dtype: the output of (token, head) is also multiplied by
+    sigmoid(gate[token, gate_offset + head]). Returns [T, Hq * dv], multiplied by ``out_scale`` before its rounding."""
     _check(q, "q", None, 3)
     _check(cache, "cache", q.dtype, 5)
     _check(positions, "positions", torch.int32, 1)
@@ -1257,9 +1347,11 @@ def attention_rows(q: torch.Tensor, cache: torch.Tensor, *, v_dim: int, position
     out = torch.empty((t, hq * v_dim), dtype=q.dtype, device=q.device)
     if t == 0:
         return out
+    _check_head_extras(q, head_sinks, gate, gate_offset)
     _run("hybrid", "ti_attention_rows", out.data_ptr(), q.data_ptr(), cache.data_ptr(), positions.data_ptr(),
          token_seq.data_ptr(), block_table.data_ptr(), block_table.shape[1], t, hq, hkv, d, v_dim, page_size, num_pages,
-         planes, float(scale), int(window or 0), int(sink is not None), float(sink or 0.0), float(out_scale), _ptr(status),
+         planes, float(scale), int(window or 0), int(sink is not None), float(sink or 0.0), _ptr(head_sinks), _ptr(gate),
+         gate.shape[1] if gate is not None else 0, int(gate_offset), float(out_scale), _ptr(status),
          _dtype_code(q), _stream())
     return out
 
@@ -1269,8 +1361,9 @@ class ScanGate:
     """How the decay of a linear-attention state is made from ``values`` (float32 [T, cols], read from column
     ``offset``). ``kind`` 'raw': the decay itself; 'sigmoid_power': sigmoid(v)^(1 / tau) per key channel;
     'step_size': dt = softplus(v + dt_bias[h]), decay exp(-exp(a_log[h]) dt) per head, and the keys are
-    multiplied by dt. ``per_channel``: one value per (head, key channel) instead of one per head."""
-    KINDS = {"raw": 0, "sigmoid_power": 1, "step_size": 2}
+    multiplied by dt; 'constant': ``values`` is one row [1, cols] of decays that every token uses (a fixed decay
+    per head, as retention has). ``per_channel``: one value per (head, key channel) instead of one per head."""
+    KINDS = {"raw": 0, "sigmoid_power": 1, "step_size": 2, "constant": 0}
 
     def __init__(self, kind: str, values: torch.Tensor, *, per_channel: bool, offset: int = 0, tau: float = 1.0,
                  a_log: Optional[torch.Tensor] = None, dt_bias: Optional[torch.Tensor] = None):
@@ -1310,8 +1403,9 @@ def linear_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gate: ScanGat
         _check(ten, name, q.dtype, 2)
     _check(gate.values, "gate", torch.float32, 2)
     t = q.shape[0]
-    if k.shape[0] != t or v.shape[0] != t or gate.values.shape[0] != t:
-        raise KernelError("linear_scan: one row per token in q, k, v and the gate")
+    constant = gate.kind == "constant"          # the one row of decays is every token's: rows lie 0 floats apart
+    if k.shape[0] != t or v.shape[0] != t or gate.values.shape[0] != (1 if constant else t):
+        raise KernelError("linear_scan: one row per token in q, k, v and the gate (one row in all for a constant gate)")
     if (q_offset + groups * key_dim > q.shape[1] or k_offset + groups * key_dim > k.shape[1]
             or v_offset + heads * value_dim > v.shape[1]
             or gate.offset + heads * (key_dim if gate.per_channel else 1) > gate.values.shape[1]):
@@ -1331,23 +1425,112 @@ def linear_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, gate: ScanGat
         fn.restype = ctypes.c_longlong
         scratch = torch.empty(int(fn(num_seqs, t, heads, key_dim, value_dim, stretches)), dtype=torch.float32, device=q.device)
     made = None          # the decays (and the keys' factors) as the scan reads them, unless the gate holds them already
-    if gate.kind != "raw" and stretches > 1:
+    if gate.kind not in ("raw", "constant") and stretches > 1:
         made = torch.empty(t * heads * (key_dim if gate.per_channel else 1) * (2 if gate.kind == "step_size" else 1),
                            dtype=torch.float32, device=q.device)
     _run("hybrid", "ti_linear_scan", out.data_ptr(), state.data_ptr(), stride, q.data_ptr(), q.shape[1], q_offset,
          k.data_ptr(), k.shape[1], k_offset, v.data_ptr(), v.shape[1], v_offset, gate.values.data_ptr(),
-         gate.values.shape[1], gate.offset, ScanGate.KINDS[gate.kind], int(gate.per_channel), float(gate.tau),
+         0 if constant else gate.values.shape[1], gate.offset, ScanGate.KINDS[gate.kind], int(gate.per_channel), float(gate.tau),
          _ptr(gate.a_log), _ptr(gate.dt_bias), _ptr(skip), float(q_scale), cu_seqlens.data_ptr(), state_slots.data_ptr(),
          num_seqs, t, heads, groups, key_dim, value_dim, stretches, _ptr(scratch),
          scratch.numel() if scratch is not None else 0, _ptr(made), _dtype_code(q), _stream())
     return out
 
 
+def head_rotation(rows: torch.Tensor, *, num_heads: int, num_kv_heads: int, head_dim: int, v_dim: int, has_kv: bool,
+                  positions: torch.Tensor, token_seq: torch.Tensor, offset: int = 0,
+                  q_norm_weight: Optional[torch.Tensor] = None, k_norm_weight: Optional[torch.Tensor] = None,
+                  eps: float = 0.0, rotation: Optional[Rotation] = None, q_scale: float = 1.0, k_scale: float = 1.0,
+                  cache: Optional[torch.Tensor] = None, block_table: Optional[torch.Tensor] = None,
+                  out_float32: bool = False, status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Per-head RMS norm (plain weights, optional), rotation and constant factors on the query heads, and with
+    ``has_kv`` the key heads, that lie in columns [offset, ...) of ``rows`` [T, cols] as [q (Hq d) | k (Hkv d) |
+    v (Hkv dv)]; values pass unchanged. With ``cache`` (planes [2, pages, Hkv, page, d] where d == dv, or rows
+    [1, pages, Hkv, page, d + dv]) keys and values go to their token's place in the pages and q [T, Hq, d] is
+    returned; without one, and with ``has_kv``, the result is the row [q | k | v] (for a recurrent mixer), float32
+    if ``out_float32``. Float32 arithmetic, one rounding."""
+    _check(rows, "rows", None, 2)
+    _check(positions, "positions", torch.int32, 1)
+    _check(token_seq, "token_seq", torch.int32, 1)
+    t = rows.shape[0]
+    nq, nk, nv = num_heads * head_dim, num_kv_heads * head_dim, num_kv_heads * v_dim
+    if offset < 0 or offset + nq + ((nk + nv) if has_kv else 0) > rows.shape[1]:
+        raise KernelError("head_rotation: the rows do not hold these heads")
+    for name, w in (("q_norm_weight", q_norm_weight), ("k_norm_weight", k_norm_weight)):
+        if w is not None:
+            _check(w, name, torch.float32, 1)
+            if w.shape[0] != head_dim:
+                raise KernelError(f"head_rotation: {name} must have head_dim entries")
+    if rotation is not None and rotation.rotary_dim > head_dim:
+        raise KernelError(f"head_rotation: rotary_dim {rotation.rotary_dim} exceeds head_dim {head_dim}")
+    planes = page_size = num_pages = 1
+    max_blocks = 0
+    if cache is not None:
+        if not has_kv:
+            raise KernelError("head_rotation: a cache is written with keys and values")
+        _check(cache, "cache", rows.dtype, 5)
+        _check(block_table, "block_table", torch.int32, 2)
+        planes = _kv_planes(cache, num_kv_heads, head_dim, v_dim)
+        num_pages, page_size, max_blocks = cache.shape[1], cache.shape[3], block_table.shape[1]
+    to_row = has_kv and cache is None
+    width = nq + nk + nv if to_row else nq
+    out_dtype = torch.float32 if out_float32 else rows.dtype
+    out = torch.empty((t, width), dtype=out_dtype, device=rows.device)
+    if t:
+        _run("hybrid", "ti_head_rotation", out.data_ptr(), width, _ptr(cache), planes, rows.data_ptr(), rows.shape[1],
+             int(offset), _ptr(q_norm_weight), _ptr(k_norm_weight), float(eps), *_rotation_args(rotation), float(q_scale),
+             float(k_scale), positions.data_ptr(), token_seq.data_ptr(), _ptr(block_table), max_blocks, t, num_heads,
+             num_kv_heads, head_dim, v_dim, int(has_kv), page_size, num_pages, _ptr(status), int(out_float32),
+             _dtype_code(rows), _stream())
+    return out if to_row else out.view(t, num_heads, head_dim)
+
+
+def delta_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay_logits: torch.Tensor, beta_logits: torch.Tensor,
+               *, a_log: torch.Tensor, dt_bias: Optional[torch.Tensor], state: torch.Tensor, heads: int, groups: int,
+               key_dim: int, value_dim: int, q_offset: int = 0, k_offset: int = 0, v_offset: int = 0,
+               decay_offset: int = 0, beta_offset: int = 0, q_scale: float = 1.0, unit_eps: float = 1e-6,
+               cu_seqlens: torch.Tensor, state_slots: torch.Tensor, num_seqs: int) -> torch.Tensor:
+    """The gated delta rule with a decay per head and key channel. Per request and head, over the step's tokens in
+    order: S <- diag(g) S, u = beta (v - S^T k), S <- S + k u^T, o = S^T q, from and back into ``state`` float32
+    [slots, heads, value_dim, key_dim] (S transposed). q and k (columns [offset, + groups * key_dim) of their tensors,
+    head h reads group h // (heads / groups)) are made unit vectors, x / sqrt(sum x^2 + unit_eps), q also times
+    ``q_scale``; g = exp(-exp(a_log[h]) * softplus(decay_logits[t, h, c] + dt_bias[h, c])) and
+    beta = sigmoid(beta_logits[t, h]) from float32 rows. Returns o float32 [T, heads * value_dim]."""
+    for name, ten in (("q", q), ("k", k), ("v", v)):
+        _check(ten, name, q.dtype, 2)
+    _check(decay_logits, "decay_logits", torch.float32, 2)
+    _check(beta_logits, "beta_logits", torch.float32, 2)
+    _check(a_log, "a_log", torch.float32, 1)
+    if dt_bias is not None:
+        _check(dt_bias, "dt_bias", torch.float32, 1)
+    t = q.shape[0]
+    if any(ten.shape[0] != t for ten in (k, v, decay_logits, beta_logits)):
+        raise KernelError("delta_scan: one row per token in q, k, v and the gates")
+    if (heads % groups or q_offset + groups * key_dim > q.shape[1] or k_offset + groups * key_dim > k.shape[1]
+            or v_offset + heads * value_dim > v.shape[1] or decay_offset + heads * key_dim > decay_logits.shape[1]
+            or beta_offset + heads > beta_logits.shape[1] or a_log.shape[0] != heads
+            or (dt_bias is not None and dt_bias.shape[0] != heads * key_dim)):
+        raise KernelError("delta_scan: the tensors do not hold these heads")
+    stride = _slot_stride(state, heads * value_dim * key_dim, "state")
+    out = torch.empty((t, heads * value_dim), dtype=torch.float32, device=q.device)
+    if t:
+        _run("hybrid", "ti_delta_scan", out.data_ptr(), state.data_ptr(), stride, q.data_ptr(), q.shape[1], int(q_offset),
+             k.data_ptr(), k.shape[1], int(k_offset), v.data_ptr(), v.shape[1], int(v_offset), decay_logits.data_ptr(),
+             decay_logits.shape[1], int(decay_offset), beta_logits.data_ptr(), beta_logits.shape[1], int(beta_offset),
+             a_log.data_ptr(), _ptr(dt_bias), float(q_scale), float(unit_eps), cu_seqlens.data_ptr(), state_slots.data_ptr(),
+             int(num_seqs), t, heads, groups, key_dim, value_dim, _dtype_code(q), _stream())
+    return out
+
+
 def gated_group_norm(y: torch.Tensor, gate: Optional[torch.Tensor], weight: torch.Tensor, *, group: int, eps: float,
-                     gate_first: bool, out_dtype: torch.dtype, gate_offset: int = 0, out_scale: float = 1.0) -> torch.Tensor:
+                     gate_first: bool, out_dtype: torch.dtype, gate_offset: int = 0, out_scale: float = 1.0,
+                     gate_activation: str = "silu") -> torch.Tensor:
     """Every ``group`` neighbouring features of y (float32 [T, C]) divided by their root mean square, times
-    ``weight`` (float32, repeated along the row if shorter) and ``out_scale``; silu of columns [gate_offset, + C) of
-    ``gate`` multiplies y before the norm (``gate_first``) or the result after it. One rounding to ``out_dtype``."""
+    ``weight`` (float32, repeated along the row if shorter) and ``out_scale``; silu (or, ``gate_activation``
+    'sigmoid', the sigmoid) of columns [gate_offset, + C) of ``gate`` multiplies y before the norm (``gate_first``)
+    or the result after it. One rounding to ``out_dtype``."""
+    if gate_activation not in ("silu", "sigmoid"):
+        raise KernelError(f"gated_group_norm: unknown gate activation {gate_activation!r}")
     _check(y, "y", torch.float32, 2)
     _check(weight, "weight", torch.float32, 1)
     t, c = y.shape
@@ -1360,7 +1543,7 @@ def gated_group_norm(y: torch.Tensor, gate: Optional[torch.Tensor], weight: torc
     out = torch.empty((t, c), dtype=out_dtype, device=y.device)
     _run("hybrid", "ti_gated_group_norm", out.data_ptr(), y.data_ptr(), _ptr(gate), gate.shape[1] if gate is not None else 0,
          gate_offset, weight.data_ptr(), weight.shape[0], t, c, group, float(eps), int(gate_first), float(out_scale),
-         _dtype_code(out), _stream())
+         int(gate_activation == "sigmoid"), _dtype_code(out), _stream())
     return out
 
 

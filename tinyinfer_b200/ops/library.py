@@ -38,11 +38,14 @@ LIBRARIES: Dict[str, dict] = {
                  headers=["common.cuh"], link=[]),
     # parts of designs with a cached latent, gated recurrences and routed experts around a float32 stream
     "latent": dict(sources=["runtime.cu", "stream.cu", "gemm_batched.cu", "latent_attention.cu",
-                            "latent_attention_mma.cu", "recurrent.cu", "experts.cu"],
+                            "latent_attention_mma.cu", "recurrent.cu"],
                    headers=["common.cuh", "mma_tile.cuh"], link=[]),
-    # parts of designs with several residual streams, short convolutions, attention over [key | value] rows and
-    # linear attention with a matrix state
-    "hybrid": dict(sources=["runtime.cu", "hyper_streams.cu", "conv_attention.cu", "linear_scan.cu"],
+    # routed experts: router, plan, grouped products, activations, combine
+    "experts": dict(sources=["runtime.cu", "experts.cu"], headers=["common.cuh", "mma_tile.cuh"], link=[]),
+    # parts of designs with several residual streams, short convolutions, attention over [key | value] rows,
+    # rotations of packed heads, and linear attention or the delta rule with a matrix state
+    "hybrid": dict(sources=["runtime.cu", "hyper_streams.cu", "conv_attention.cu", "linear_scan.cu", "head_rotation.cu",
+                            "delta_scan.cu"],
                    headers=["common.cuh"], link=[]),
     # bfloat16 tensor-core kernels (tcgen05 + TMA); only a bfloat16 model loads it
     "sm100": dict(sources=["runtime.cu", "sm100_host.cu", "gemm_tcgen05.cu", "attention_mma.cu",

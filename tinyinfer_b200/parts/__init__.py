@@ -2,8 +2,8 @@ from .base import (Block, CacheNeed, FeedForward, Mixer, Norm, Part, PositionEnc
                    TensorSpec, state_slices, build_block, build_feed_forward, build_mixer, build_norm,
                    build_position, register_block, register_feed_forward, register_mixer,
                    register_norm, register_position)
-from . import (attention, block, conv_attention, experts, feedforward, latent_attention, linear_attention, norm,  # noqa: F401
-               parallel, position, recurrence, state_space)  # noqa: F401  (register the built-in parts)
+from . import (attention, block, conv_attention, delta, experts, feedforward, latent_attention, linear_attention, norm,  # noqa: F401
+               parallel, position, recurrence, retention, state_space)  # noqa: F401  (register the built-in parts)
 
 __all__ = [
     "Block", "CacheNeed", "FeedForward", "Mixer", "Norm", "Part", "PositionEncoding", "StateNeed",

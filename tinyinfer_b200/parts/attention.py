@@ -4,6 +4,13 @@ Order of operations as in the reference (tinyinfer/models/qwen3.py:106-132): pac
 projection, per-head RMSNorm of q and k, rotation, append of k and v to the cache, attention of
 every token over its own request's keys, output projection. The q, k and v matrices are packed
 row-wise as [q; k; v] like the reference's loader does (tinyinfer/utils/loader.py:52-96).
+
+Beyond the reference's layer the spec may ask for: values of another size than the keys (``v_dim``), a rotation of
+only the first features of a head, a learned sink per query head in the softmax denominator (``head_sinks``), an
+output gate sigmoid(W_g x)_h per (token, head) (``head_gate``: W_g's rows ride in the packed projection), and a
+layer without key/value tensors that reads what another layer cached (``shares_cache``). Such a layer runs
+``_attend_general``: packed product [q | k | v | g], per-head norm + rotation + append (``ops.head_rotation``),
+attention with the sinks and the gate in its epilogue.
 """
 from __future__ import annotations
 
@@ -23,22 +30,37 @@ class Attention(Mixer):
         self.position = build_position(spec.position, dtype, device)
         self._rotation = self.position.rotation()      # opaque here: the kernel reads it
         self.w_qkv = self.b_qkv = self.w_o = self.b_o = None
-        self.q_norm = self.k_norm = None
+        self.q_norm = self.k_norm = self.sinks = None
+        self._general = bool(spec.value_dim != spec.head_dim or spec.head_sinks or spec.head_gate or spec.shares_cache)
+        if self._general and (spec.bias or spec.window):
+            raise ValueError("biases and windows are not combined with value sizes, sinks, gates or shared caches")
+        short = spec.short_names
+        self._n = {"q": "q" if short else "q_proj.weight", "k": "k" if short else "k_proj.weight",
+                   "v": "v" if short else "v_proj.weight", "o": "o" if short else "o_proj.weight",
+                   "q_norm": "q.norm" if short else "q_norm.weight", "k_norm": "k.norm" if short else "k_norm.weight",
+                   "sink": "sink" if short else "sinks", "g": "g" if short else "g_proj.weight"}
 
     def cache_need(self):
-        return CacheNeed(self.spec.num_kv_heads, self.spec.head_dim, self.spec.window)
+        s = self.spec
+        if s.value_dim != s.head_dim:       # keys and values of different sizes lie side by side in one row a token
+            return CacheNeed(s.num_kv_heads, s.head_dim + s.value_dim, s.window, planes=1)
+        return CacheNeed(s.num_kv_heads, s.head_dim, s.window)
 
     def tensors(self):
-        s = self.spec
-        t = {
-            "q_proj.weight": TensorSpec((s.q_size, s.hidden_size)),
-            "k_proj.weight": TensorSpec((s.kv_size, s.hidden_size)),
-            "v_proj.weight": TensorSpec((s.kv_size, s.hidden_size)),
-            "o_proj.weight": TensorSpec((s.hidden_size, s.q_size)),
-        }
+        s, n = self.spec, self._n
+        t = {n["q"]: TensorSpec((s.q_size, s.hidden_size))}
+        if not s.shares_cache:
+            t[n["k"]] = TensorSpec((s.kv_size, s.hidden_size))
+            t[n["v"]] = TensorSpec((s.num_kv_heads * s.value_dim, s.hidden_size))
+        t[n["o"]] = TensorSpec((s.hidden_size, s.num_heads * s.value_dim))
         if s.qk_norm is not None:
-            t["q_norm.weight"] = TensorSpec((s.head_dim,), role="vector32", init="ones_noise")
-            t["k_norm.weight"] = TensorSpec((s.head_dim,), role="vector32", init="ones_noise")
+            t[n["q_norm"]] = TensorSpec((s.head_dim,), role="vector32", init="ones_noise")
+            if not s.shares_cache:
+                t[n["k_norm"]] = TensorSpec((s.head_dim,), role="vector32", init="ones_noise")
+        if s.head_sinks:
+            t[n["sink"]] = TensorSpec((s.num_heads,), role="vector32")
+        if s.head_gate:
+            t[n["g"]] = TensorSpec((s.num_heads, s.hidden_size))
         if s.bias:
             t["q_proj.bias"] = TensorSpec((s.q_size,), role="vector32")
             t["k_proj.bias"] = TensorSpec((s.kv_size,), role="vector32")
@@ -47,20 +69,52 @@ class Attention(Mixer):
         return t
 
     def load(self, tensors):
-        s = self.spec
-        self.w_qkv = torch.cat([tensors["q_proj.weight"], tensors["k_proj.weight"],
-                                tensors["v_proj.weight"]], dim=0).contiguous()
-        self.w_o = tensors["o_proj.weight"].contiguous()
+        s, n = self.spec, self._n
+        rows = [tensors[n["q"]]] + ([] if s.shares_cache else [tensors[n["k"]], tensors[n["v"]]])
+        if s.head_gate:
+            # the gate's rows follow q, k and v; zero rows fill the packed matrix up to a multiple of eight rows,
+            # which the tensor-core product wants of its output's row length
+            gate = tensors[n["g"]]
+            fill = (-(sum(r.shape[0] for r in rows) + gate.shape[0])) % 8
+            rows += [gate] + ([gate.new_zeros((fill, gate.shape[1]))] if fill else [])
+        self.w_qkv = torch.cat(rows, dim=0).contiguous()
+        self.w_o = tensors[n["o"]].contiguous()
         if s.qk_norm is not None:
-            self.q_norm = tensors["q_norm.weight"]
-            self.k_norm = tensors["k_norm.weight"]
+            self.q_norm = tensors[n["q_norm"]]
+            self.k_norm = None if s.shares_cache else tensors[n["k_norm"]]
+        if s.head_sinks:
+            self.sinks = tensors[n["sink"]].contiguous()
         if s.bias:
             self.b_qkv = torch.cat([tensors["q_proj.bias"], tensors["k_proj.bias"],
                                     tensors["v_proj.bias"]]).contiguous()
             self.b_o = tensors["o_proj.bias"]
 
+    def _attend_general(self, x, step, cache):
+        s = self.spec
+        own = not s.shares_cache
+        if own != bool(cache.writes):
+            raise ValueError("a layer with key/value tensors writes its cache entry; one without them only reads")
+        packed = ops.linear(x, self.w_qkv)                   # [T, q | (k | v) | (g) | fill]
+        gate_at = s.q_size + ((s.kv_size + s.num_kv_heads * s.value_dim) if own else 0)
+        q = ops.head_rotation(packed, num_heads=s.num_heads, num_kv_heads=s.num_kv_heads, head_dim=s.head_dim,
+                              v_dim=s.value_dim, has_kv=own, positions=step.positions, token_seq=step.token_seq,
+                              q_norm_weight=self.q_norm, k_norm_weight=self.k_norm,
+                              eps=s.qk_norm.eps if s.qk_norm is not None else 0.0, rotation=self._rotation,
+                              cache=cache.kv if own else None, block_table=cache.block_table, status=step.status)
+        extras = dict(head_sinks=self.sinks, gate=packed if s.head_gate else None, gate_offset=gate_at)
+        if cache.kv.shape[0] == 2:          # keys and values of one size: the paged attention, tensor cores where the sizes allow
+            return ops.paged_attention(q, cache.kv, positions=step.positions, token_seq=step.token_seq,
+                                       block_table=cache.block_table, scale=s.scale, step=step, status=step.status,
+                                       **extras)
+        return ops.attention_rows(q, cache.kv, v_dim=s.value_dim, positions=step.positions, token_seq=step.token_seq,
+                                  block_table=cache.block_table, scale=s.scale, step=step, status=step.status, **extras)
+
     def _attend(self, x, step, cache, link=None, link_eps=0.0):
         s = self.spec
+        if self._general:
+            if link is not None:
+                raise ValueError("this attention layer takes its input normed")
+            return self._attend_general(x, step, cache)
         qkv = (ops.linear(x, self.w_qkv, bias=self.b_qkv) if link is None
                else ops.linear(x, self.w_qkv, bias=self.b_qkv, link=link, link_eps=link_eps))
         q = ops.qk_norm_rope_append(
@@ -82,7 +136,7 @@ class Attention(Mixer):
 
     def forward_prenorm(self, x, norm, link, next_norm, step, cache):
         rms = norm.as_rms()
-        if rms is None or not ops.norm_link_ok(x):
+        if rms is None or self._general or not ops.norm_link_ok(x):
             return super().forward_prenorm(x, norm, link, next_norm, step, cache)
         # few tokens: the packed projection takes the norm's second half (if the product before left the
         # first), and the output projection leaves the first half of the norm that follows

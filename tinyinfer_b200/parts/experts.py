@@ -2,6 +2,13 @@
 softmax scores; their outputs are weighted by those scores over their sum; optionally a shared expert runs for
 every token. An expert is down(act(up h)), act(v) = max(v, 0)^2, no biases.
 
+The spec may change each of these: ``activation`` 'clamped_glu' (an expert has a gate and an up matrix:
+g = min(W_gate h, limit), u = clamp(W_up h, -limit, limit), down(g * sigmoid(alpha g) * (u + 1))), ``identity_experts``
+(the router's last outputs stand for experts whose output is their input; they have no tensors), ``score_correction``
+(a learned number per router output steers the choice, the weights stay the plain scores), ``renormalize`` False (the
+weights are the chosen scores themselves) and ``router_input`` 'input' (the router reads the sublayer's normed input
+instead of the float32 stream).
+
 A step's (token, choice) pairs are put in expert order on the device and the experts run as two grouped
 products over row tiles; nothing is read back to the host and no token is ever dropped, so a token's result
 does not depend on what else is in the batch. The part sits in blocks whose norm follows the sublayer
@@ -21,17 +28,28 @@ class Experts(FeedForward):
 
     def __init__(self, spec, dtype, device):
         super().__init__(spec, dtype, device)
-        if spec.activation != "relu_squared":
-            raise ValueError(f"activation {spec.activation!r} is not supported (relu_squared only)")
-        self.w_router = self.w_up = self.w_down = self.w_shared_up = self.w_shared_down = None
+        if spec.activation not in ("relu_squared", "clamped_glu"):
+            raise ValueError(f"activation {spec.activation!r} is not supported (relu_squared, clamped_glu)")
+        if spec.activation == "clamped_glu" and not spec.glu_limit > 0:
+            raise ValueError("clamped_glu needs a positive limit")
+        if spec.identity_experts < 0 or spec.top > spec.num_experts + spec.identity_experts:
+            raise ValueError("top exceeds the number of router outputs")
+        if spec.shared_size and spec.activation != "relu_squared":
+            raise ValueError("a shared expert is built with the relu_squared activation only")
+        self.glu = spec.activation == "clamped_glu"
+        self.w_router = self.w_up = self.w_down = self.w_shared_up = self.w_shared_down = self.correction = None
 
     def tensors(self):
         s = self.spec
         t = {}
         for e in range(s.num_experts):
+            if self.glu:
+                t[f"e{e}.gate"] = TensorSpec((s.expert_size, s.hidden_size))
             t[f"e{e}.up"] = TensorSpec((s.expert_size, s.hidden_size))
             t[f"e{e}.down"] = TensorSpec((s.hidden_size, s.expert_size))
-        t["router"] = TensorSpec((s.num_experts, s.hidden_size))
+        t["router"] = TensorSpec((s.num_experts + s.identity_experts, s.hidden_size))
+        if s.score_correction:
+            t["correction"] = TensorSpec((s.num_experts + s.identity_experts,), role="vector32")
         if s.shared_size:
             t["shared.up"] = TensorSpec((s.shared_size, s.hidden_size))
             t["shared.down"] = TensorSpec((s.hidden_size, s.shared_size))
@@ -39,7 +57,13 @@ class Experts(FeedForward):
 
     def load(self, tensors):
         s = self.spec
-        self.w_up = torch.stack([tensors[f"e{e}.up"] for e in range(s.num_experts)]).contiguous()
+        if self.glu:       # an expert's rows: [gate | up], one grouped product for both
+            self.w_up = torch.stack([torch.cat([tensors[f"e{e}.gate"], tensors[f"e{e}.up"]], dim=0)
+                                     for e in range(s.num_experts)]).contiguous()
+        else:
+            self.w_up = torch.stack([tensors[f"e{e}.up"] for e in range(s.num_experts)]).contiguous()
+        if s.score_correction:
+            self.correction = tensors["correction"].contiguous()
         self.w_down = torch.stack([tensors[f"e{e}.down"] for e in range(s.num_experts)]).contiguous()
         self.w_router = tensors["router"].contiguous()
         if s.shared_size:
@@ -51,8 +75,13 @@ class Experts(FeedForward):
         s = self.spec
         # the more rows an expert gets, the taller the row tiles its grouped products are planned with
         routing = ops.route_experts(x32, self.w_router, s.top, s.weight_eps,
-                                    tile_rows=ops.expert_tile_rows(x, s.num_experts, s.top, s.expert_size))
-        hidden = ops.expert_linear(x, self.w_up, routing, up=True)
+                                    tile_rows=ops.expert_tile_rows(x, s.num_experts, s.top, s.expert_size),
+                                    correction=self.correction, renormalize=s.renormalize, real_experts=s.num_experts)
+        if self.glu:
+            hidden = ops.clamped_glu(ops.expert_linear(x, self.w_up, routing, up=True, activation=False),
+                                     s.glu_limit, s.glu_alpha)
+        else:
+            hidden = ops.expert_linear(x, self.w_up, routing, up=True)
         down = ops.expert_linear(hidden, self.w_down, routing, up=False)
         shared = None
         if s.shared_size:
@@ -65,18 +94,22 @@ class Experts(FeedForward):
         rms = norm.as_rms()
         if rms is None:
             raise ValueError("the experts' fused output needs an RMSNorm behind them")
-        routing, down, shared = self._experts(x32, x)
+        if self.spec.identity_experts:
+            raise ValueError("identity experts are not built into the fused output of this arrangement")
+        routing, down, shared = self._experts(x if self.spec.router_input == "input" else x32, x)
         return ops.experts_combine_norm_add(x32, down, shared, routing, rms[0], rms[1], self.dtype)
 
     def forward(self, x, step=None):
-        """The plain sum, for arrangements that keep the stream in the compute dtype."""
-        x32 = x if x.dtype == torch.float32 else x.float()
-        routing, down, shared = self._experts(x32, x)
-        rows = down[routing.slot_of.long().view(-1)].view(x.shape[0], self.spec.top, -1)
-        out = (rows * routing.weight[:, :, None]).sum(dim=1)
+        """The plain weighted sum in the compute dtype, for arrangements whose residual work is not the experts'
+        business. The router reads ``x`` (its logits are float32 all the same)."""
+        s = self.spec
+        if s.identity_experts and s.router_input != "input":
+            raise ValueError("identity experts pass the sublayer's input on, which is also what the router must read")
+        routing, down, shared = self._experts(x if s.router_input == "input" or x.dtype == torch.float32 else x.float(), x)
+        out = ops.experts_combine(down, x, routing, s.num_experts)
         if shared is not None:
-            out = out + shared.float()
-        return out.to(x.dtype)
+            out = ops.add(out, shared)
+        return out
 
 
 register_feed_forward("experts", Experts)

@@ -20,16 +20,17 @@ class GatedMLP(FeedForward):
 
     def tensors(self):
         s = self.spec
+        gate, up, down = s.names
         return {
-            "gate_proj.weight": TensorSpec((s.intermediate_size, s.hidden_size)),
-            "up_proj.weight": TensorSpec((s.intermediate_size, s.hidden_size)),
-            "down_proj.weight": TensorSpec((s.hidden_size, s.intermediate_size)),
+            gate: TensorSpec((s.intermediate_size, s.hidden_size)),
+            up: TensorSpec((s.intermediate_size, s.hidden_size)),
+            down: TensorSpec((s.hidden_size, s.intermediate_size)),
         }
 
     def load(self, tensors):
-        self.w_gate_up = torch.cat([tensors["gate_proj.weight"], tensors["up_proj.weight"]],
-                                   dim=0).contiguous()
-        self.w_down = tensors["down_proj.weight"].contiguous()
+        gate, up, down = self.spec.names
+        self.w_gate_up = torch.cat([tensors[gate], tensors[up]], dim=0).contiguous()
+        self.w_down = tensors[down].contiguous()
 
     def forward(self, x, step=None):
         return ops.linear(ops.gated_linear(x, self.w_gate_up), self.w_down)

@@ -13,10 +13,15 @@ class RMSNorm(Norm):
         self.weight = None
 
     def tensors(self):
-        return {self.spec.tensor: TensorSpec((self.spec.size,), role="vector32", init="ones_noise")}
+        # a weight stored around zero (the norm multiplies by offset + w) is drawn around zero too
+        init = "ones_noise" if not getattr(self.spec, "offset", 0.0) else "normal"
+        return {self.spec.tensor: TensorSpec((self.spec.size,), role="vector32", init=init)}
 
     def load(self, tensors):
         self.weight = tensors[self.spec.tensor]
+        offset = float(getattr(self.spec, "offset", 0.0))
+        if offset:
+            self.weight = (self.weight + offset).contiguous()      # float32: the sum is made once, here
 
     def forward(self, x):
         return ops.rmsnorm(x, self.weight, self.spec.eps)
