@@ -22,7 +22,9 @@ CPU implementation of the tests, in seconds, beside the engine's time for the sa
 decode throughput of the Gulisun design (latent attention, gated recurrences, routed experts) at two sizes with
 the layer sizes of real models, each beside the Qwen3 preset of the same width and number of layers;
 ``--design ravutar`` does the same for the Ravutar design (attention with short convolutions and a sink beside gated
-linear attention, state-space layers, several residual streams).
+linear attention, state-space layers, several residual streams), and ``--design sinulix`` for the Sinulix design
+(attention with head sinks and gates, retention, the channel-wise delta rule, clamped-GLU experts), which also runs
+the Ravutar preset of the same width, the nearest design with matrix-state layers, for the kernel-by-kernel comparison.
 
 ``--impl reference`` runs the unmodified reference project from ``baseline/_ref`` through its own
 public API (``tinyinfer.LLM(Config(...))``, ``add_request``, ``step``) on a model folder of the same
@@ -572,10 +574,55 @@ def ravutar_numbers(cfg, batch, context):
     return dict(macs=macs, attn_per_key=attn_per_key, head=head, step_bytes=step_bytes, scan_flops=scan_flops)
 
 
+def sinulix_numbers(cfg, batch, context):
+    """As ``ravutar_numbers`` for the Sinulix design: matrix elements a token multiplies (active experts only),
+    attention flops per key, flops a token spends in the matrix-state recurrences (retention: decay, write and
+    read-out; the delta rule: decay, S^T k, the write and the read-out), and the bytes a decode step must move (dense
+    weights, the experts a batch of this size is expected to touch, the head, the cached keys and values of every
+    attention layer, shared or not, every request's matrix states read and written)."""
+    w, macs, dense, expert_bytes, attn_per_key, scan_flops, cache_per_token, state_bytes = cfg.width, 0, 0, 0.0, 0.0, 0.0, 0, 0
+    for layer in cfg.layers:
+        m, f = layer["mixer"], layer.get("mlp")
+        h, d, v = m["heads"], m["dim"], m["vdim"]
+        if layer["type"] == "attention":
+            g = m["kv_heads"]
+            own = 0 if m.get("kv_from") is not None else g * (d + v)
+            part = w * (h * d + own + h) + w * h * v
+            attn_per_key += 2.0 * h * (d + v)
+            cache_per_token += g * (d + v) * 2
+        elif layer["type"] == "retention":
+            part = w * (2 * h * d + 2 * h * v) + w * h * v
+            scan_flops += 5.0 * h * d * v
+            state_bytes += h * d * v * 4 * 2
+        else:
+            g, rank = m["kv_heads"], m.get("gate_rank", 16)
+            part = w * (2 * g * d + h * v + h) + rank * (2 * w + h * d + h * v) + w * h * v
+            scan_flops += 7.0 * h * d * v
+            state_bytes += h * d * v * 4 * 2
+        macs += part
+        dense += part
+        if f is not None and f["kind"] == "dense":
+            macs += 3 * f["ff"] * w
+            dense += 3 * f["ff"] * w
+        elif f is not None:
+            e, top, ff = f["router"]["experts"], f["router"]["top"], f["expert"]["ff"]
+            outputs = e + f["router"].get("identity", 0)
+            macs += top * 3 * ff * w + outputs * w          # an upper bound: a chosen identity expert multiplies nothing
+            dense += outputs * w
+            touched = e * (1.0 - (1.0 - min(1.0, top / outputs)) ** batch)
+            expert_bytes += touched * 3 * ff * w * 2
+    head = cfg.vocab * w
+    step_bytes = dense * 2 + expert_bytes + head * 2 + batch * context * cache_per_token + batch * state_bytes
+    return dict(macs=macs, attn_per_key=attn_per_key, head=head, step_bytes=step_bytes, scan_flops=scan_flops)
+
+
 DESIGNS = {      # design -> (what its numbers are made with, [(its preset, the Qwen3 preset of the same width)])
     "gulisun": (gulisun_numbers, (("gulisun-1b", "0.6b"), ("gulisun-2b", "1.7b"))),
     "ravutar": (ravutar_numbers, (("ravutar-1b", "0.6b"), ("ravutar-2b", "1.7b"))),
+    "sinulix": (sinulix_numbers, (("sinulix-1b", "0.6b"), ("sinulix-2b", "1.7b"))),
 }
+SIBLINGS = {"sinulix-1b": ("ravutar", "ravutar-1b"), "sinulix-2b": ("ravutar", "ravutar-2b")}   # also measured beside it
+
 
 
 def measure_design(cfg, peaks, flops_of_prefill, bytes_of_step, batch, context, steps, warmup, prefill_tokens):
@@ -655,6 +702,15 @@ def design_comparison(args) -> int:
                                       qn["weight_bytes"] + batch * context * qn["kv_bytes_per_token"], batch, context,
                                       steps, warmup, prefill_tokens)
         row["qwen3"]["preset"] = theirs
+        if ours in SIBLINGS:
+            kind, preset = SIBLINGS[ours]
+            sib = preset_config(preset)
+            sn = DESIGNS[kind][0](sib, batch, context)
+            sflops = (2.0 * sn["macs"] * t + sn["attn_per_key"] * t * (t + 1) / 2.0 + 2.0 * sn["head"]
+                      + sn.get("scan_flops", 0.0) * t)
+            row[kind] = measure_design(sib, peaks, sflops, sn["step_bytes"], batch, context, steps, warmup, prefill_tokens)
+            row[kind]["preset"] = preset
+            row[kind]["layers"] = len(sib.run_order()) if hasattr(sib, "run_order") else len(sib.layers)
         row["prefill_ratio"] = row[design]["prefill_tok_s"] / row["qwen3"]["prefill_tok_s"]
         row["decode_ratio"] = row[design]["decode_tok_s"] / row["qwen3"]["decode_tok_s"]
         sizes[ours] = row
@@ -679,7 +735,7 @@ def main() -> int:
     ap.add_argument("--skip-points", action="store_true", help="only the headline batch")
     ap.add_argument("--skip-extras", action="store_true", help="leave out the 'configs' of the line")
     ap.add_argument("--extras", default="32b,mix,cpu", help="which of the other configurations to run")
-    ap.add_argument("--design", default="", choices=["", "gulisun", "ravutar"],
+    ap.add_argument("--design", default="", choices=["", "gulisun", "ravutar", "sinulix"],
                     help="instead of the headline: prefill and decode of this design beside Qwen3 at equal size")
     ap.add_argument("--ref-block-size", type=int, default=256, help="reference arm: its kvcache_block_size (its default)")
     ap.add_argument("--ref-step-tokens", type=int, default=32,
