@@ -97,7 +97,7 @@ _SIGNATURES = {
                              c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p],
         "ti_delta_scan": [c_void_p, c_void_p, c_ll, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int,
                           c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_float, c_float, c_void_p,
-                          c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+                          c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_ll, c_int, c_void_p],
         "ti_streams_step": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int,
                             c_int, c_int, c_int, c_int, c_int, c_void_p],
         "ti_gelu": [c_void_p, c_void_p, c_ll, c_int, c_int, c_void_p],
@@ -1514,11 +1514,14 @@ def delta_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay_logits: 
     stride = _slot_stride(state, heads * value_dim * key_dim, "state")
     out = torch.empty((t, heads * value_dim), dtype=torch.float32, device=q.device)
     if t:
+        # what the recurrence reads of every token, made once: unit q and k, the decays, v, beta and k.q, float32
+        work = torch.empty(t * (2 * groups * key_dim + heads * (key_dim + value_dim + 1) + groups) + 24,
+                           dtype=torch.float32, device=q.device)
         _run("hybrid", "ti_delta_scan", out.data_ptr(), state.data_ptr(), stride, q.data_ptr(), q.shape[1], int(q_offset),
              k.data_ptr(), k.shape[1], int(k_offset), v.data_ptr(), v.shape[1], int(v_offset), decay_logits.data_ptr(),
              decay_logits.shape[1], int(decay_offset), beta_logits.data_ptr(), beta_logits.shape[1], int(beta_offset),
              a_log.data_ptr(), _ptr(dt_bias), float(q_scale), float(unit_eps), cu_seqlens.data_ptr(), state_slots.data_ptr(),
-             int(num_seqs), t, heads, groups, key_dim, value_dim, _dtype_code(q), _stream())
+             int(num_seqs), t, heads, groups, key_dim, value_dim, work.data_ptr(), work.numel(), _dtype_code(q), _stream())
     return out
 
 
