@@ -58,6 +58,19 @@ cudaError_t ti_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t sm
     return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
 
+// The same without the attribute: the kernel starts when the stream's earlier work has ended, on an empty machine,
+// so its blocks are dealt evenly to the SMs. For a long kernel of few blocks whose warps wait on latency: started
+// early, its blocks land wherever the kernel before frees room first, several on one SM, and stay there.
+template <typename... KArgs, typename... Args>
+cudaError_t ti_launch_alone(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 template <typename T> __device__ __forceinline__ float to_f32(T v);
 template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
 template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }

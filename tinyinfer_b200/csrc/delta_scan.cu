@@ -3,7 +3,7 @@
 // transposed, [H][dv][dk], as linear_scan.cu keeps its states), zero when the request starts. For every token, in order:
 //     S <- diag(g) S            u = beta * (v - S^T k)            S <- S + k u^T            o = S^T q
 // so the read-out sees the token's own write. Two kernels, all in float32:
-//   delta_prepare_kernel, a block a token, makes what does not depend on the state, once for all columns:
+//   delta_prepare_kernel, a block a token and head, makes what does not depend on the state, once for all columns:
 //     q, k   : the group's rows divided by sqrt(sum(x^2) + unit_eps), q also times q_scale; and their product k.q
 //     g      : exp(-exp(A_log[h]) * softplus(a[t][h][c] + dt_bias[h][c]))        a: float32 rows (a projection's output)
 //     beta   : sigmoid(b[t][h])                                                    b: float32 rows
@@ -18,7 +18,7 @@
 #include "common.cuh"
 
 constexpr int DS_MAX_WARPS = 4;
-constexpr int DP_THREADS = 256;
+constexpr int DP_THREADS = 128;
 
 __device__ __forceinline__ float ds_softplus(float x) { return fmaxf(x, 0.f) + log1pf(expf(-fabsf(x))); }
 
@@ -46,14 +46,15 @@ template <typename T>
 __global__ void __launch_bounds__(DP_THREADS) delta_prepare_kernel(DeltaPrepArgs a) {
     ti_grid_launch_dependents();
     ti_grid_wait();
-    const int t = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, warps = DP_THREADS / 32;
-    const T* q = (const T*)a.q + (size_t)t * a.ld_q + a.q_off;
-    const T* k = (const T*)a.k + (size_t)t * a.ld_k + a.k_off;
-    const T* v = (const T*)a.v + (size_t)t * a.ld_v + a.v_off;
-    for (int g = warp; g < a.groups; g += warps) {       // unit vectors: a warp a group
+    const int t = blockIdx.x, h = blockIdx.y, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int per_group = a.heads / a.groups;
+    if (warp == 0 && h % per_group == 0) {               // unit vectors: the first head of a group makes them
+        const int g = h / per_group;
+        const T* q = (const T*)a.q + (size_t)t * a.ld_q + a.q_off + g * a.dk;
+        const T* k = (const T*)a.k + (size_t)t * a.ld_k + a.k_off + g * a.dk;
         float ssq = 0.f, ssk = 0.f, sqk = 0.f;
         for (int c = lane; c < a.dk; c += 32) {
-            const float qv = to_f32(q[g * a.dk + c]), kv = to_f32(k[g * a.dk + c]);
+            const float qv = to_f32(q[c]), kv = to_f32(k[c]);
             ssq = fmaf(qv, qv, ssq);
             ssk = fmaf(kv, kv, ssk);
         }
@@ -61,7 +62,7 @@ __global__ void __launch_bounds__(DP_THREADS) delta_prepare_kernel(DeltaPrepArgs
         ssk = warp_sum(ssk);
         const float fq = a.q_scale / sqrtf(ssq + a.unit_eps), fk = 1.f / sqrtf(ssk + a.unit_eps);
         for (int c = lane; c < a.dk; c += 32) {
-            const float qv = to_f32(q[g * a.dk + c]) * fq, kv = to_f32(k[g * a.dk + c]) * fk;
+            const float qv = to_f32(q[c]) * fq, kv = to_f32(k[c]) * fk;
             a.w.q[((size_t)t * a.groups + g) * a.dk + c] = qv;
             a.w.k[((size_t)t * a.groups + g) * a.dk + c] = kv;
             sqk = fmaf(qv, kv, sqk);
@@ -69,14 +70,14 @@ __global__ void __launch_bounds__(DP_THREADS) delta_prepare_kernel(DeltaPrepArgs
         sqk = warp_sum(sqk);
         if (lane == 0) a.w.kq[(size_t)t * a.groups + g] = sqk;
     }
-    const int hk = a.heads * a.dk, hv = a.heads * a.dv;
-    for (int e = tid; e < hk; e += DP_THREADS) {
-        const float z = a.a[(size_t)t * a.ld_a + a.a_off + e] + (a.dt_bias ? a.dt_bias[e] : 0.f);
-        a.w.g[(size_t)t * hk + e] = expf(-expf(a.a_log[e / a.dk]) * ds_softplus(z));
+    const float rate = expf(a.a_log[h]);
+    for (int c = tid; c < a.dk; c += DP_THREADS) {
+        const float z = a.a[(size_t)t * a.ld_a + a.a_off + h * a.dk + c] + (a.dt_bias ? a.dt_bias[h * a.dk + c] : 0.f);
+        a.w.g[((size_t)t * a.heads + h) * a.dk + c] = expf(-rate * ds_softplus(z));
     }
-    for (int e = tid; e < hv; e += DP_THREADS) a.w.v[(size_t)t * hv + e] = to_f32(v[e]);
-    for (int h = tid; h < a.heads; h += DP_THREADS)
-        a.w.beta[(size_t)t * a.heads + h] = 1.f / (1.f + expf(-a.b[(size_t)t * a.ld_b + a.b_off + h]));
+    const T* v = (const T*)a.v + (size_t)t * a.ld_v + a.v_off + h * a.dv;
+    for (int c = tid; c < a.dv; c += DP_THREADS) a.w.v[((size_t)t * a.heads + h) * a.dv + c] = to_f32(v[c]);
+    if (tid == 0) a.w.beta[(size_t)t * a.heads + h] = 1.f / (1.f + expf(-a.b[(size_t)t * a.ld_b + a.b_off + h]));
 }
 
 __device__ __forceinline__ void ds_copy16(float* dst, const float* src) {
@@ -94,19 +95,18 @@ struct DeltaScanArgs {
     float* state;                 // slot s at state + s * slot_stride: [H][dv][dk]
     long long slot_stride;
     const int *cu_seqlens, *state_slots;
-    int heads, groups, dk, dv, kp, chunk;
+    int heads, groups, dk, dv, chunk;
     int vec_k, vec_v;             // rows of dk floats, and a block's columns of v, move in 16-byte pieces
 };
 
-template <int KPT>
+template <int KPT, int KP>
 __global__ void __launch_bounds__(DS_MAX_WARPS * 32) delta_scan_kernel(DeltaScanArgs a) {
     extern __shared__ __align__(16) float smem[];
-    ti_grid_launch_dependents();
-    const int KP = a.kp;
     constexpr int PITCH = KPT + 4;                       // floats from one lane part's rows to the next: no two lanes in a bank
-    const int trow = KP * PITCH;
+    constexpr int trow = KP * PITCH;
+    constexpr int cols_per_warp = 32 / KP;
     const int threads = blockDim.x, warps = threads >> 5;
-    const int cols_per_warp = 32 / KP, cpb = warps * cols_per_warp;
+    const int cpb = warps * cols_per_warp;
     const int col_blocks = (a.dv + cpb - 1) / cpb;
     const int h = blockIdx.x / col_blocks, cb = blockIdx.x % col_blocks;
     const int seq = blockIdx.y;
@@ -118,6 +118,14 @@ __global__ void __launch_bounds__(DS_MAX_WARPS * 32) delta_scan_kernel(DeltaScan
     const int g = h / (a.heads / a.groups);
     const int buf_floats = (a.chunk * (3 * trow + cpb + 2) + 3) & ~3;
     for (int e = tid; e < 2 * buf_floats; e += threads) smem[e] = 0.f;   // the rows past dk stay zero
+    // which pieces of a token's rows this thread fetches: piece p_first (and every `threads`-th after it) of the
+    // tokens tt_first, tt_first + tt_step, ...; with more threads than pieces, several tokens side by side
+    const int step = a.vec_k ? 4 : 1, pieces = (a.dk + step - 1) / step;
+    const bool wide = threads >= pieces;
+    const int tt_step = wide ? threads / pieces : 1;
+    const int tt_first = wide ? tid / pieces : 0;
+    const int p_first = wide ? tid % pieces : tid;
+    const int vstep = a.vec_v ? 4 : 1, vpieces = cpb / vstep;
     __syncthreads();
     ti_grid_wait();
     const int row0 = a.cu_seqlens[seq], row1 = a.cu_seqlens[seq + 1];
@@ -134,18 +142,24 @@ __global__ void __launch_bounds__(DS_MAX_WARPS * 32) delta_scan_kernel(DeltaScan
         float* sv = sg + (size_t)a.chunk * trow;         // [chunk][cpb]
         float* sb = sv + (size_t)a.chunk * cpb;          // [chunk]
         float* sx = sb + a.chunk;                        // [chunk]: k.q
-        const int step = a.vec_k ? 4 : 1, pieces = (a.dk + step - 1) / step;
-        for (int e = tid; e < n * pieces; e += threads) {
-            const int tt = e / pieces, idx = (e % pieces) * step;
-            const size_t t = (size_t)(t0 + tt);
-            const int at = tt * trow + (idx / KPT) * PITCH + idx % KPT;
-            const float* gq = a.w.q + (t * a.groups + g) * a.dk + idx;
-            const float* gk = a.w.k + (t * a.groups + g) * a.dk + idx;
-            const float* gg = a.w.g + (t * a.heads + h) * a.dk + idx;
-            if (a.vec_k) { ds_copy16(sq + at, gq); ds_copy16(sk + at, gk); ds_copy16(sg + at, gg); }
-            else { ds_copy4(sq + at, gq); ds_copy4(sk + at, gk); ds_copy4(sg + at, gg); }
+        if (tt_first < tt_step) {
+            const size_t ld_qk = (size_t)a.groups * a.dk, ld_g = (size_t)a.heads * a.dk;
+            for (int p = p_first; p < pieces; p += threads) {
+                const int idx = p * step;
+                int at = tt_first * trow + (idx / KPT) * PITCH + idx % KPT;
+                const float* gq = a.w.q + ((size_t)(t0 + tt_first) * a.groups + g) * a.dk + idx;
+                const float* gk = a.w.k + ((size_t)(t0 + tt_first) * a.groups + g) * a.dk + idx;
+                const float* gg = a.w.g + ((size_t)(t0 + tt_first) * a.heads + h) * a.dk + idx;
+                for (int tt = tt_first; tt < n; tt += tt_step) {
+                    if (a.vec_k) { ds_copy16(sq + at, gq); ds_copy16(sk + at, gk); ds_copy16(sg + at, gg); }
+                    else { ds_copy4(sq + at, gq); ds_copy4(sk + at, gk); ds_copy4(sg + at, gg); }
+                    at += tt_step * trow;
+                    gq += tt_step * ld_qk;
+                    gk += tt_step * ld_qk;
+                    gg += tt_step * ld_g;
+                }
+            }
         }
-        const int vstep = a.vec_v ? 4 : 1, vpieces = cpb / vstep;
         for (int e = tid; e < n * vpieces; e += threads) {
             const int tt = e / vpieces, c = (e % vpieces) * vstep;
             if (cb * cpb + c >= a.dv) continue;
@@ -195,6 +209,7 @@ __global__ void __launch_bounds__(DS_MAX_WARPS * 32) delta_scan_kernel(DeltaScan
                 }
             }
             float dot = dk0 + dk1, oq = dq0 + dq1;
+#pragma unroll
             for (int off = 1; off < KP; off <<= 1) {
                 dot += __shfl_xor_sync(0xffffffffu, dot, off);
                 oq += __shfl_xor_sync(0xffffffffu, oq, off);
@@ -207,6 +222,7 @@ __global__ void __launch_bounds__(DS_MAX_WARPS * 32) delta_scan_kernel(DeltaScan
         __syncthreads();                                 // the chunk has been read: its buffer may be filled again
     }
     ds_wait<0>();
+    ti_grid_launch_dependents();                         // only now: the walk is long, and the next kernel's blocks would sit on the SMs through it
     if (col_ok) {
 #pragma unroll
         for (int r = 0; r < KPT; ++r)
@@ -249,30 +265,43 @@ TI_API int ti_delta_scan(float* y, float* state, long long slot_stride, const vo
     w.beta = w.kq + ds_round4(t * groups);
     DeltaPrepArgs prep = {w, q, k, v, ld_q, q_off, ld_k, k_off, ld_v, v_off, a, ld_a, a_off, b, ld_b, b_off,
                           a_log, dt_bias, q_scale, unit_eps, heads, groups, dk, dv};
-    if (dtype == TI_F32) ti_launch(delta_prepare_kernel<float>, dim3(num_tokens), DP_THREADS, 0, stream, prep);
-    else ti_launch(delta_prepare_kernel<__nv_bfloat16>, dim3(num_tokens), DP_THREADS, 0, stream, prep);
+    TI_REQUIRE(heads <= 65535, "delta_scan: too many heads");
+    if (dtype == TI_F32) ti_launch(delta_prepare_kernel<float>, dim3(num_tokens, heads), DP_THREADS, 0, stream, prep);
+    else ti_launch(delta_prepare_kernel<__nv_bfloat16>, dim3(num_tokens, heads), DP_THREADS, 0, stream, prep);
     TI_CHECK_LAUNCH("delta_prepare");
 
     int kp = 1;
-    while (kp < 32 && (dk + kp - 1) / kp > 16) kp <<= 1;
+    const int rows = 8;                                  // most rows of a column that a lane holds
+    while (kp < 32 && (dk + kp - 1) / kp > rows) kp <<= 1;
     const int per_lane = (dk + kp - 1) / kp;
     const int kpt = per_lane <= 4 ? 4 : per_lane <= 8 ? 8 : per_lane <= 16 ? 16 : 32;
-    // few columns a block when the step has few (request, head) pairs, so that more SMs have a block
+    // few columns a block when the step has few (request, head) pairs, so that every SM has a block; many columns a
+    // block otherwise, as every block fetches the head's q, k and g for itself
     int warps = DS_MAX_WARPS;
-    while (warps > 1 && (long long)num_seqs * heads * ((dv + warps * (32 / kp) - 1) / (warps * (32 / kp))) < 2 * 148) warps >>= 1;
+    while (warps > 1 && (long long)num_seqs * heads * ((dv + warps * (32 / kp) - 1) / (warps * (32 / kp))) < 148) warps >>= 1;
     const int trow = kp * (kpt + 4), cpb = warps * (32 / kp);
     // two buffers of `chunk` tokens within the 48 KB that need no opt-in; a step of single tokens stages no more than one
     int chunk = 16;
     while (chunk > 1 && 2 * ds_round4((size_t)chunk * (3 * trow + cpb + 2)) * sizeof(float) > 44 * 1024) chunk >>= 1;
     if (num_tokens == num_seqs) chunk = 1;
     const size_t smem = 2 * ds_round4((size_t)chunk * (3 * trow + cpb + 2)) * sizeof(float);
-    DeltaScanArgs args = {w, y, state, slot_stride, cu_seqlens, state_slots, heads, groups, dk, dv, kp, chunk,
+    DeltaScanArgs args = {w, y, state, slot_stride, cu_seqlens, state_slots, heads, groups, dk, dv, chunk,
                           dk % 4 == 0, dv % 4 == 0 && cpb % 4 == 0};
     dim3 grid(heads * ((dv + cpb - 1) / cpb), num_seqs);
-    if (kpt == 4) ti_launch(delta_scan_kernel<4>, grid, warps * 32, smem, stream, args);
-    else if (kpt == 8) ti_launch(delta_scan_kernel<8>, grid, warps * 32, smem, stream, args);
-    else if (kpt == 16) ti_launch(delta_scan_kernel<16>, grid, warps * 32, smem, stream, args);
-    else ti_launch(delta_scan_kernel<32>, grid, warps * 32, smem, stream, args);
+    // a walk of many tokens starts alone (see ti_launch_alone); a step of single tokens is short and starts early
+    const bool alone = num_tokens != num_seqs;
+    bool launched = false;
+#define TI_DSCAN(KPT, KP)                                                                         \
+    if (!launched && kpt == KPT && kp == KP) {                                                    \
+        if (alone) ti_launch_alone(delta_scan_kernel<KPT, KP>, grid, warps * 32, smem, stream, args); \
+        else ti_launch(delta_scan_kernel<KPT, KP>, grid, warps * 32, smem, stream, args);         \
+        launched = true;                                                                          \
+    }
+#define TI_DSCAN_ROWS(KPT) TI_DSCAN(KPT, 1) TI_DSCAN(KPT, 2) TI_DSCAN(KPT, 4) TI_DSCAN(KPT, 8) TI_DSCAN(KPT, 16) TI_DSCAN(KPT, 32)
+    TI_DSCAN_ROWS(4) TI_DSCAN_ROWS(8) TI_DSCAN_ROWS(16) TI_DSCAN(32, 32)
+#undef TI_DSCAN_ROWS
+#undef TI_DSCAN
+    TI_REQUIRE(launched, "delta_scan: no kernel for %d rows a lane over %d lanes", kpt, kp);
     TI_CHECK_LAUNCH("delta_scan");
     return 0;
 }
