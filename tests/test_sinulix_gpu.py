@@ -64,8 +64,9 @@ def delta_plain(q, k, v, g, beta, S):
                                                 (4, 4, 64, 64), (2, 2, 128, 128), (4, 1, 12, 36)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_delta_scan_against_plain(heads, groups, dk, dv, dtype):
-    """Two requests of unequal length in two calls (a prompt's portion, then a portion beside one decoded token):
-    the state goes through slots that lie inside a larger state, with someone else's floats in front."""
+    """Two requests of unequal length in three calls (a prompt's portion, then a portion beside one decoded token, then
+    a portion of many of the kernel's chunks beside a short one): the state goes through slots that lie inside a
+    larger state, with someone else's floats in front."""
     from tinyinfer_b200 import ops
     gen = torch.Generator().manual_seed(heads * dk + dv)
     pad = 5
@@ -74,7 +75,7 @@ def test_delta_scan_against_plain(heads, groups, dk, dv, dtype):
     view = state_d[:, 11:].unflatten(1, (heads, dv, dk))
     S = [torch.zeros(heads, dk, dv, dtype=torch.float64) for _ in range(2)]
     per = heads // groups
-    for lens in ([37, 5], [1, 22]):
+    for lens in ([37, 5], [1, 22], [3, 141]):
         T = sum(lens)
         row = torch.randn(T, pad + 2 * groups * dk + heads * dv, generator=gen).to(dtype)
         a = torch.randn(T, 3 + heads * dk, generator=gen)
