@@ -182,6 +182,9 @@ ATTENTION_SHAPES = [
     (8, 2, 64, 64, 16, [(130, 130), (129, 1), (200, 2)]),                 # two planes: the tensor-core kernels
     (8, 4, 128, 128, 64, [(1500, 1), (1, 1), (256, 1), (257, 1), (700, 513)]),
     (4, 4, 128, 128, 64, [(1300, 897), (64, 64), (65, 1)]),
+    (6, 2, 64, 64, 16, [(150, 150), (131, 1), (90, 3)]),                   # odd numbers of query heads a key head
+    (5, 1, 128, 128, 32, [(300, 1), (70, 70), (33, 2)]),
+    (14, 2, 64, 64, 64, [(200, 1), (129, 129)]),
 ]
 
 
