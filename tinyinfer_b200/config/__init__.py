@@ -7,10 +7,11 @@ from .qwen3 import Qwen3Config
 from .gulisun import GulisunConfig
 from .ravutar import RavutarConfig
 from .sinulix import SinulixConfig
+from .fezozen import FezozenConfig
 
 __all__ = [
     "EngineConfig", "parse_dtype", "Architecture", "architecture_of", "known_architectures",
     "known_presets", "load_config", "lookup_architecture", "preset_config", "register_architecture", "AttentionSpec", "ExecStep",
     "GatedMLPSpec", "LayerSpec", "ModelSpec", "NormSpec", "PositionSpec", "TensorNames",
-    "default_execution", "Qwen3Config", "GulisunConfig", "RavutarConfig", "SinulixConfig",
+    "default_execution", "Qwen3Config", "GulisunConfig", "RavutarConfig", "SinulixConfig", "FezozenConfig",
 ]

@@ -23,14 +23,29 @@ class NormSpec:
 
 
 @dataclass(frozen=True)
+class FrequencyBlend:
+    """Stretches a rotary encoding beyond the length it was made for (the YaRN recipe): with
+    pair(t) = rotary_dim * ln(original / (2 pi t)) / (2 ln theta), the pair index that makes t full turns over
+    ``original`` positions, lo = max(floor(pair(fast)), 0), hi = min(ceil(pair(slow)), rotary_dim - 1) and
+    ramp_j = clamp((j - lo) / max(hi - lo, 0.001), 0, 1), pair j turns at f_j / factor * ramp_j + f_j * (1 - ramp_j),
+    and every cosine and sine is multiplied by 0.1 * ln(factor) + 1."""
+    factor: float
+    original: int
+    fast: float
+    slow: float
+
+
+@dataclass(frozen=True)
 class PositionSpec:
-    """How positions enter a mixer. ``kind='rope'``: half-split rotation of the first
-    ``rotary_dim`` features of every head with inv_freq[j] = theta ** (-2j / rotary_dim).
-    ``kind='none'``: positions are not used."""
+    """How positions enter a mixer. ``kind='rope'``: rotation of the first ``rotary_dim`` features of every head
+    with inv_freq[j] = theta ** (-2j / rotary_dim), in pairs (j, j + rotary_dim / 2) or, ``interleaved``,
+    (2j, 2j + 1). ``kind='none'``: positions are not used."""
     kind: str = "rope"
     theta: float = 10000.0
     rotary_dim: int = 0
     exact_frequencies: bool = False         # inv_freq worked out in float64 and rounded once (default: in float32)
+    interleaved: bool = False
+    blend: Optional[FrequencyBlend] = None  # frequencies slowed down for lengths beyond the original one
 
 
 @dataclass(frozen=True)
@@ -51,6 +66,10 @@ class AttentionSpec:
     head_gate: bool = False                 # head h's output is multiplied by sigmoid(W_g x)_h, one number per head
     shares_cache: bool = False              # no key/value tensors: the layer reads the keys and values another layer caches
     short_names: bool = False               # tensors are 'q', 'k', 'v', 'o', 'q.norm', 'k.norm', 'sink', 'g'
+    qkv_bias: bool = False                  # biases on q, k and v alone (the tensor's name with '.b' added), none on o
+    softcap: Optional[float] = None         # a score s becomes softcap * tanh(s / softcap) before the softmax
+    qk_unit_norm: Optional[float] = None    # eps: q and k are divided by their root mean square per head (no weight)
+                                            # AFTER the rotation
 
     @property
     def q_size(self) -> int:
@@ -96,6 +115,8 @@ class LatentAttentionSpec:
     shares_cache: bool = False
     window: Optional[int] = None
     kind: str = "latent_attention"
+    output_gate: bool = False               # the heads side by side are multiplied by sigmoid(W_g h), feature by feature
+    # q_rank 0: the queries have no latent: q = W_q h (tensor "q") in place of "dq", "dq.norm" and "uq"
 
 
 @dataclass(frozen=True)
@@ -132,6 +153,9 @@ class ExpertsSpec:
     score_correction: bool = False          # a learned number per router output is added to the scores for the CHOICE only
     renormalize: bool = True                # False: the weights are the chosen scores themselves, not divided by their sum
     router_input: str = "stream"            # 'stream': the router reads the float32 residual; 'input': the sublayer's input
+    # activation 'silu_glu': an expert is down(silu(gate h) * (up h))
+    scoring: str = "softmax"                # 'sigmoid': an expert's score is the sigmoid of its own router logit
+    weight_input: bool = False              # the weight multiplies what the expert READS (expert(w h)), not its output
 
 
 @dataclass(frozen=True)
@@ -264,7 +288,11 @@ class LayerSpec:
     through its norm and writes back into all of them (``learned_mixing``: the block owns the coefficients
     ``hc1.*`` for the mixer and ``hc2.*`` for the feed-forward; otherwise all are 1, which with one stream is the
     pre-norm residual kept in float32).
-    ``feed_forward`` None (with ``feed_forward_norm`` None): the block has a mixer only."""
+    ``feed_forward`` None (with ``feed_forward_norm`` None): the block has a mixer only.
+    ``mixer_out_norm`` / ``feed_forward_out_norm`` ('multi_stream' only): a second norm on the sublayer's OUTPUT
+    before it is added, x += norm_b(sublayer(norm(x))); its ``tensor`` is the name behind the LAYER's prefix.
+    ``index``: the number in this layer's checkpoint names where that is not its place in ``ModelSpec.layers`` (a model
+    that lists, among its layers, some that run another layer's tensors has fewer layers with tensors than numbers)."""
     mixer: object
     feed_forward: object
     mixer_norm: NormSpec
@@ -272,6 +300,9 @@ class LayerSpec:
     arrangement: str = "pre_norm"
     streams: int = 1
     learned_mixing: bool = False
+    mixer_out_norm: Optional[NormSpec] = None
+    feed_forward_out_norm: Optional[NormSpec] = None
+    index: Optional[int] = None
 
 
 @dataclass(frozen=True)

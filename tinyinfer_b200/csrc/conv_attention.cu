@@ -376,7 +376,7 @@ __global__ void __launch_bounds__(AR_THREADS) attention_rows_kernel(
     const int* __restrict__ token_seq, const int* __restrict__ block_table, int max_blocks, int hq, int hkv, int d, int dv,
     int page_size, int num_pages, int row, long long v_off, float scale, int window, int has_sink, float sink,
     const float* __restrict__ head_sinks, const T* __restrict__ gate, int ld_gate, int gate_off,
-    float out_scale, int* __restrict__ status) {
+    float out_scale, float softcap, int* __restrict__ status) {
     __shared__ float qs[AR_MAX_D];
     __shared__ float p[AR_THREADS];
     __shared__ long long row_off[AR_THREADS];
@@ -413,6 +413,7 @@ __global__ void __launch_bounds__(AR_THREADS) attention_rows_kernel(
                 float dot = 0.f;
                 for (int i = 0; i < d; ++i) dot = fmaf(qs[i], to_f32(krow[i]), dot);
                 s = dot * scale;
+                if (softcap > 0.f) s = softcap * tanhf(s / softcap);      // scores level off smoothly at +-softcap
             } else if (status) {
                 atomicExch(status, 2);                 // a visible key without a page
             }
@@ -449,30 +450,31 @@ __global__ void __launch_bounds__(AR_THREADS) attention_rows_kernel(
 // planes 1: cache [pages][hkv][page_size][d + dv]; planes 2 (d == dv): [2][pages][hkv][page_size][d].
 // out: [T][hq * dv], multiplied by out_scale before its one rounding. head_sinks (float32 [hq], or null): a sink's
 // logit per query head in place of the one `sink`; gate (compute dtype, rows of ld_gate, first column gate_off, or
-// null): the output of (token, head) is also multiplied by sigmoid(gate[token][head]).
+// null): the output of (token, head) is also multiplied by sigmoid(gate[token][head]). softcap > 0: a score s becomes
+// softcap * tanh(s / softcap) before the softmax.
 TI_API int ti_attention_rows(void* out, const void* q, const void* cache, const int* positions, const int* token_seq,
                              const int* block_table, int max_blocks, int num_tokens, int hq, int hkv, int d, int dv,
                              int page_size, int num_pages, int planes, float scale, int window, int has_sink, float sink,
                              const float* head_sinks, const void* gate, int ld_gate, int gate_off,
-                             float out_scale, int* status, int dtype, cudaStream_t stream) {
+                             float out_scale, float softcap, int* status, int dtype, cudaStream_t stream) {
     TI_REQUIRE(planes == 1 || (planes == 2 && d == dv), "attention_rows: two planes need keys and values of one size");
     const int row = planes == 2 ? d : d + dv;
     const long long v_off = planes == 2 ? (long long)num_pages * hkv * page_size * d : d;
     TI_REQUIRE(d > 0 && d <= AR_MAX_D && dv > 0 && dv <= AR_MAX_D, "attention_rows: head sizes %d / %d not in 1..%d", d, dv, AR_MAX_D);
     TI_REQUIRE(hq > 0 && hkv > 0 && hq % hkv == 0, "attention_rows: %d query heads do not group over %d kv heads", hq, hkv);
-    TI_REQUIRE(page_size > 0 && num_tokens >= 0 && window >= 0, "attention_rows: bad sizes");
+    TI_REQUIRE(page_size > 0 && num_tokens >= 0 && window >= 0 && softcap >= 0.f, "attention_rows: bad sizes");
     TI_REQUIRE(num_tokens <= 65535, "attention_rows: more than 65535 tokens in one step");
     if (num_tokens == 0) return 0;
     dim3 grid(hq, num_tokens);
     if (dtype == TI_F32)
         ti_launch(attention_rows_kernel<float>, grid, AR_THREADS, 0, stream, (float*)out, (const float*)q, (const float*)cache,
                   positions, token_seq, block_table, max_blocks, hq, hkv, d, dv, page_size, num_pages, row, v_off, scale, window,
-                  has_sink, sink, head_sinks, (const float*)gate, ld_gate, gate_off, out_scale, status);
+                  has_sink, sink, head_sinks, (const float*)gate, ld_gate, gate_off, out_scale, softcap, status);
     else if (dtype == TI_BF16)
         ti_launch(attention_rows_kernel<__nv_bfloat16>, grid, AR_THREADS, 0, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)q,
                   (const __nv_bfloat16*)cache, positions, token_seq, block_table, max_blocks, hq, hkv, d, dv, page_size,
                   num_pages, row, v_off, scale, window, has_sink, sink, head_sinks, (const __nv_bfloat16*)gate, ld_gate, gate_off,
-                  out_scale, status);
+                  out_scale, softcap, status);
     else TI_REQUIRE(false, "attention_rows: unknown dtype %d", dtype);
     TI_CHECK_LAUNCH("attention_rows");
     return 0;

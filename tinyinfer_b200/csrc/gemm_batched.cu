@@ -3,7 +3,8 @@
 // of a block-diagonal gate matrix (the block is the batch). Every operand has a row stride and a batch stride, so
 // heads or blocks that lie side by side in a row of a [tokens, features] tensor are read and written where they are.
 // float32 FMA accumulation in a fixed k order; a row's result does not depend on which other rows share its tile.
-// act: 0 none, 1 logistic sigmoid.
+// act: 0 none, 1 logistic sigmoid. gate (may be null; the operands' dtype, rows of ldg elements, batch b's columns from
+// b * sg on): the result is multiplied by sigmoid(gate[m][b * sg + n]), an output gate that another product made.
 #include "common.cuh"
 #include "mma_tile.cuh"
 
@@ -12,6 +13,7 @@ constexpr int GB_BM = 64, GB_BN = 64, GB_BK = 16, GB_THREADS = 256;
 struct GbShape {
     int M, N, K;
     long long ldx, sx, ldw, sw, ldo, so, sbias;
+    const void* gate; long long ldg, sg;
 };
 
 template <typename T, typename OutT, int ACT>
@@ -65,6 +67,7 @@ __global__ void __launch_bounds__(GB_THREADS) gemm_batched_kernel(
             float v = acc[i][j];
             if (bias) v += bias[(size_t)b * s.sbias + n];
             if (ACT == 1) v = 1.f / (1.f + expf(-v));
+            if (s.gate) v *= 1.f / (1.f + expf(-to_f32(((const T*)s.gate)[(size_t)m * s.ldg + (size_t)b * s.sg + n])));
             out[(size_t)m * s.ldo + n] = from_f32<OutT>(v);
         }
     }
@@ -97,6 +100,7 @@ __global__ void __launch_bounds__(mt::THREADS) gemm_batched_mma_kernel(
             float u = v[e];
             if (bias) u += bias[(size_t)b * s.sbias + n + e];
             if (ACT == 1) u = 1.f / (1.f + expf(-u));
+            if (s.gate) u *= 1.f / (1.f + expf(-__bfloat162float(((const __nv_bfloat16*)s.gate)[(size_t)m * s.ldg + (size_t)b * s.sg + n + e])));
             out[(size_t)m * s.ldo + n + e] = from_f32<OutT>(u);
         }
     });
@@ -104,14 +108,15 @@ __global__ void __launch_bounds__(mt::THREADS) gemm_batched_mma_kernel(
 
 TI_API int ti_gemm_batched(void* out, const void* x, const void* w, const float* bias, int batch, int M, int N, int K,
                            long long ldx, long long sx, long long ldw, long long sw, long long ldo, long long so,
-                           long long sbias, int act, int out_f32, int dtype, cudaStream_t stream) {
+                           long long sbias, int act, int out_f32, const void* gate, long long ldg, long long sg, int dtype,
+                           cudaStream_t stream) {
     TI_REQUIRE(batch > 0 && M >= 0 && N > 0 && K > 0, "gemm_batched: bad sizes");
     TI_REQUIRE(act == 0 || act == 1, "gemm_batched: unknown activation %d", act);
     TI_REQUIRE(batch <= 65535, "gemm_batched: too many batches");
     if (M == 0) return 0;
     dim3 grid((N + GB_BN - 1) / GB_BN, (M + GB_BM - 1) / GB_BM, batch);
     TI_REQUIRE(grid.y <= 65535, "gemm_batched: too many rows");
-    GbShape s{M, N, K, ldx, sx, ldw, sw, ldo, so, sbias};
+    GbShape s{M, N, K, ldx, sx, ldw, sw, ldo, so, sbias, gate, ldg, sg};
     typedef __nv_bfloat16 B;
 #define GB_LAUNCH(T, O, A) ti_launch(gemm_batched_kernel<T, O, A>, grid, GB_THREADS, 0, stream, (O*)out, (const T*)x, (const T*)w, bias, s)
     if (dtype == TI_F32) {

@@ -5,7 +5,9 @@
 //         features and Hkv heads of dv value features
 //   q, k: optional RMS norm over the head with a plain weight, then the rotation of the first rotary_dim features
 //         (same rotation data as rope_append.cu: inverse frequencies or a table of cosines and sines, half-split or
-//         interleaved pairs), then a constant factor (q_scale, k_scale); v passes unchanged
+//         interleaved pairs; rot_factor multiplies every cosine and sine), then a constant factor (q_scale, k_scale);
+//         v passes unchanged. norm_after != 0: the RMS norm comes AFTER the rotation instead, with the weight or, if
+//         there is none, without one (x / rms(x))
 //   out : q goes to out[t][head * d] (rows of ld_out). With a cache, k and v go to the token's place in its page:
 //         planes 2 (d == dv): [2][pages][Hkv][page][d]; planes 1: rows [k (d) | v (dv)]. Without a cache and with
 //         has_kv, k and v follow q in the row of out: [q | k | v], so that a recurrent mixer reads them from there.
@@ -22,7 +24,7 @@ struct HeadRotationArgs {
     const void* in; int ld_in, in_off;
     const float *q_w, *k_w; float eps;
     const float *inv_freq, *table; int table_positions, interleaved, rotary_dim;
-    float q_scale, k_scale;
+    float q_scale, k_scale, rot_factor; int norm_after;
     const int *positions, *token_seq, *block_table; int max_blocks;
     int hq, hkv, d, dv, has_kv, page_size, num_pages;
     int* status;
@@ -31,6 +33,7 @@ struct HeadRotationArgs {
 template <typename T, typename OutT>
 __global__ void __launch_bounds__(HR_WARPS * 32) head_rotation_kernel(HeadRotationArgs a) {
     __shared__ float buf[HR_WARPS][HR_MAX_D];
+    __shared__ float turned[HR_WARPS][HR_MAX_D];
     ti_grid_launch_dependents();
     ti_grid_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -52,7 +55,8 @@ __global__ void __launch_bounds__(HR_WARPS * 32) head_rotation_kernel(HeadRotati
         ss += v * v;
     }
     const float* w = is_q ? a.q_w : (is_k ? a.k_w : nullptr);
-    if (w != nullptr) {
+    const bool norm_last = a.norm_after && (is_q || is_k);
+    if (w != nullptr && !norm_last) {
         ss = warp_sum(ss);
         const float inv = rsqrtf(ss / (float)size + a.eps);
         for (int i = lane; i < size; i += 32) x[i] = w[i] * x[i] * inv;
@@ -83,6 +87,8 @@ __global__ void __launch_bounds__(HR_WARPS * 32) head_rotation_kernel(HeadRotati
     }
     const int half = a.rotary_dim >> 1;
     const float pos_f = (float)pos;
+    float* y = turned[warp];
+    float ss_after = 0.f;
     for (int i = lane; i < size; i += 32) {
         float o = x[i];
         if (rotate && i < a.rotary_dim) {
@@ -96,8 +102,18 @@ __global__ void __launch_bounds__(HR_WARPS * 32) head_rotation_kernel(HeadRotati
             } else {
                 sincosf(pos_f * a.inv_freq[j], &s, &c);
             }
+            c *= a.rot_factor;
+            s *= a.rot_factor;
             o = first ? x[i] * c - x[other] * s : x[i] * c + x[other] * s;
         }
+        y[i] = o;                                   // read back by this lane alone
+        ss_after += o * o;
+    }
+    float inv_after = 1.f;
+    if (norm_last) inv_after = rsqrtf(warp_sum(ss_after) / (float)size + a.eps);
+    for (int i = lane; i < size; i += 32) {
+        float o = y[i];
+        if (norm_last) o = (w != nullptr ? w[i] : 1.f) * o * inv_after;
         o *= factor;
         if (cdst) cdst[i] = from_f32<T>(o);
         else odst[i] = from_f32<OutT>(o);
@@ -107,10 +123,10 @@ __global__ void __launch_bounds__(HR_WARPS * 32) head_rotation_kernel(HeadRotati
 // dtype: of `in` and of the cache; out_f32 != 0: `out` is float32 whatever the dtype.
 TI_API int ti_head_rotation(void* out, int ld_out, void* cache, int planes, const void* in, int ld_in, int in_off,
                             const float* q_norm_w, const float* k_norm_w, float eps, const float* inv_freq,
-                            const float* cos_sin_table, int table_positions, int interleaved, int rotary_dim, float q_scale,
+                            const float* cos_sin_table, int table_positions, int interleaved, int rotary_dim, float rot_factor, float q_scale,
                             float k_scale, const int* positions, const int* token_seq, const int* block_table,
                             int max_blocks, int num_tokens, int hq, int hkv, int d, int dv, int has_kv, int page_size,
-                            int num_pages, int* status, int out_f32, int dtype, cudaStream_t stream) {
+                            int num_pages, int* status, int out_f32, int norm_after, int dtype, cudaStream_t stream) {
     TI_REQUIRE(d > 0 && d <= HR_MAX_D && dv > 0 && dv <= HR_MAX_D, "head_rotation: head sizes %d / %d not in 1..%d", d, dv, HR_MAX_D);
     TI_REQUIRE(rotary_dim >= 0 && rotary_dim <= d && rotary_dim % 2 == 0,
                "head_rotation: rotary_dim %d must be even and at most the head size %d", rotary_dim, d);
@@ -123,7 +139,7 @@ TI_API int ti_head_rotation(void* out, int ld_out, void* cache, int planes, cons
     if (num_tokens == 0) return 0;
     HeadRotationArgs a = {out, ld_out, cache, planes, (long long)num_pages * hkv * page_size * d, in, ld_in, in_off,
                           q_norm_w, k_norm_w, eps, inv_freq, cos_sin_table, table_positions, interleaved, rotary_dim,
-                          q_scale, k_scale, positions, token_seq, block_table, max_blocks, hq, hkv, d, dv, has_kv ? 1 : 0,
+                          q_scale, k_scale, rot_factor, norm_after ? 1 : 0, positions, token_seq, block_table, max_blocks, hq, hkv, d, dv, has_kv ? 1 : 0,
                           page_size, num_pages, status};
     const int heads_total = hq + (has_kv ? 2 * hkv : 0);
     dim3 grid((heads_total + HR_WARPS - 1) / HR_WARPS, num_tokens);

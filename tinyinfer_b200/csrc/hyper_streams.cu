@@ -81,7 +81,8 @@ template <typename TY, typename TH, int VEC, int NS>
 __global__ void __launch_bounds__(VEC == 4 ? 256 : 512) streams_step_kernel(float* __restrict__ X, const TY* __restrict__ y, const float* __restrict__ c_mix,
                                     const float* __restrict__ c_out, const float* __restrict__ c_in,
                                     const float* __restrict__ norm_w, float eps, TH* __restrict__ h,
-                                    const int* __restrict__ rows, int num_tokens, int width, int streams) {
+                                    const int* __restrict__ rows, int num_tokens, int width, int streams,
+                                    const float* __restrict__ upd_w, float upd_eps) {
     extern __shared__ float urow[];
     __shared__ float red[33];
     __shared__ float mix[HS_MAX_STREAMS * HS_MAX_STREAMS], cout_s[HS_MAX_STREAMS], cin_s[HS_MAX_STREAMS];
@@ -95,6 +96,17 @@ __global__ void __launch_bounds__(VEC == 4 ? 256 : 512) streams_step_kernel(floa
     __syncthreads();
     const int r = blockIdx.x;
     const int t = rows ? rows[r] : r;
+    float y_inv = 1.f;
+    if (y && upd_w) {                 // the update passes an RMS norm of its own first: its row's mean square
+        float sy = 0.f;
+        for (int i = threadIdx.x * VEC; i < width; i += blockDim.x * VEC) {
+            float yv[VEC];
+            HsVec<VEC>::load(y + (size_t)t * width + i, yv);
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) sy += yv[e] * yv[e];
+        }
+        y_inv = rsqrtf(block_sum(sy, red) / (float)width + upd_eps);
+    }
     float ss = 0.f;
     for (int i = threadIdx.x * VEC; i < width; i += blockDim.x * VEC) {
         float x[NS][VEC];
@@ -104,6 +116,12 @@ __global__ void __launch_bounds__(VEC == 4 ? 256 : 512) streams_step_kernel(floa
         if (y) {
             float yv[VEC], fresh[NS][VEC];
             HsVec<VEC>::load(y + (size_t)t * width + i, yv);
+            if (upd_w) {
+                float uw[VEC];
+                HsVec<VEC>::load(upd_w + i, uw);
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) yv[e] = uw[e] * yv[e] * y_inv;
+            }
 #pragma unroll
             for (int to = 0; to < NS; ++to) {
                 if (to < streams) {
@@ -151,16 +169,18 @@ __global__ void __launch_bounds__(VEC == 4 ? 256 : 512) streams_step_kernel(floa
 
 // y (may be null: nothing pending) with c_mix [S][S] (indexed [from][to]) and c_out [S]; h (may be null: only the
 // update) with c_in [S] and norm_w [W]. rows (may be null): the tokens to work on; h then has one row per entry.
+// upd_w (may be null; float32 [W]) with upd_eps: y is replaced by upd_w * y * rsqrt(mean(y^2) + upd_eps) before it is
+// applied (a norm on a sublayer's output).
 TI_API int ti_streams_step(float* X, const void* y, const float* c_mix, const float* c_out, const float* c_in,
                            const float* norm_w, float eps, void* h, const int* rows, int num_rows, int num_tokens, int width,
-                           int streams, int y_dtype, int h_dtype, cudaStream_t stream) {
+                           int streams, int y_dtype, int h_dtype, const float* upd_w, float upd_eps, cudaStream_t stream) {
     TI_REQUIRE(num_rows >= 0 && num_tokens >= 0 && width > 0 && streams >= 1 && streams <= HS_MAX_STREAMS,
                "streams_step: bad sizes (1..%d streams)", HS_MAX_STREAMS);
     TI_REQUIRE(width <= 48 * 1024 / 4, "streams_step: rows of %d features do not fit shared memory", width);
     TI_REQUIRE(!y || (c_mix && c_out), "streams_step: an update needs its coefficients");
     TI_REQUIRE(!h || (c_in && norm_w), "streams_step: a read needs its coefficients and the norm's weight");
     if (num_rows == 0 || (!y && !h)) return 0;
-    const bool wide = width % 4 == 0 && ((uintptr_t)X | (uintptr_t)y | (uintptr_t)h | (uintptr_t)norm_w) % 16 == 0 &&
+    const bool wide = width % 4 == 0 && ((uintptr_t)X | (uintptr_t)y | (uintptr_t)h | (uintptr_t)norm_w | (uintptr_t)upd_w) % 16 == 0 &&
                       ((size_t)num_tokens * width) % 4 == 0;
     int threads = 64;
     while (threads < (wide ? 256 : 512) && threads * 4 < width) threads <<= 1;
@@ -168,7 +188,7 @@ TI_API int ti_streams_step(float* X, const void* y, const float* c_mix, const fl
     typedef __nv_bfloat16 B;
 #define TI_STEP_N(TY, TH, VEC, NS)                                                                                        \
     ti_launch(streams_step_kernel<TY, TH, VEC, NS>, num_rows, threads, smem, stream, X, (const TY*)y, c_mix, c_out, c_in, \
-              norm_w, eps, (TH*)h, rows, num_tokens, width, streams)
+              norm_w, eps, (TH*)h, rows, num_tokens, width, streams, upd_w, upd_eps)
 #define TI_STEP_V(TY, TH, VEC)                             \
     do {                                                   \
         if (streams == 1) TI_STEP_N(TY, TH, VEC, 1);       \

@@ -21,6 +21,7 @@ struct LaRotation {                 // as in rope_append.cu: angle p * inv_freq[
     const float* inv_freq;
     const float* table;
     int table_positions, interleaved, rotary_dim;
+    float factor;                   // multiplies every cosine and sine (1: a plain rotation)
 };
 
 // Feature i of a vector x[0..n) at position pos after the rotation of its first rotary_dim features.
@@ -37,6 +38,8 @@ __device__ __forceinline__ float la_rotated(const float* x, int i, int pos, cons
     } else {
         sincosf((float)pos * r.inv_freq[j], &s, &c);
     }
+    c *= r.factor;
+    s *= r.factor;
     return first ? x[i] * c - x[other] * s : x[i] * c + x[other] * s;
 }
 
@@ -58,11 +61,13 @@ __global__ void __launch_bounds__(LP_THREADS) latent_prepare_kernel(
     for (int i = tid; i < width; i += LP_THREADS) row[i] = down[(size_t)t * ld + i];
     __syncthreads();
     float ss = 0.f;
-    for (int i = tid; i < q_rank; i += LP_THREADS) ss += row[i] * row[i];
-    ss = block_sum(ss, red);
-    const float inv_q = rsqrtf(ss / (float)q_rank + eps);
-    for (int i = tid; i < q_rank; i += LP_THREADS)
-        q_latent[(size_t)t * q_rank + i] = from_f32<T>(q_w[i] * row[i] * inv_q);
+    if (q_rank > 0) {                                  // q_rank 0: the queries have no latent of their own
+        for (int i = tid; i < q_rank; i += LP_THREADS) ss += row[i] * row[i];
+        ss = block_sum(ss, red);
+        const float inv_q = rsqrtf(ss / (float)q_rank + eps);
+        for (int i = tid; i < q_rank; i += LP_THREADS)
+            q_latent[(size_t)t * q_rank + i] = from_f32<T>(q_w[i] * row[i] * inv_q);
+    }
     if (cache == nullptr) return;                      // a layer that reads another layer's cache
     const float* kv = row + q_rank;
     ss = 0.f;
@@ -87,15 +92,16 @@ __global__ void __launch_bounds__(LP_THREADS) latent_prepare_kernel(
 
 TI_API int ti_latent_prepare(void* q_latent, void* cache, const float* down, int ld, const float* q_w, const float* kv_w,
                              float eps, int q_rank, int rank, int rot, const float* inv_freq, const float* table,
-                             int table_positions, int interleaved, int rotary_dim, const int* positions,
+                             int table_positions, int interleaved, int rotary_dim, float rot_factor, const int* positions,
                              const int* token_seq, const int* block_table, int max_blocks, int num_tokens, int page_size,
                              int num_pages, int* status, int dtype, cudaStream_t stream) {
-    TI_REQUIRE(num_tokens >= 0 && q_rank > 0 && rank > 0 && rot >= 0, "latent_prepare: bad sizes");
+    TI_REQUIRE(num_tokens >= 0 && q_rank >= 0 && rank > 0 && rot >= 0, "latent_prepare: bad sizes");
+    TI_REQUIRE(q_rank == 0 || (q_latent && q_w), "latent_prepare: a query latent needs its output and its norm's weight");
     TI_REQUIRE(rotary_dim >= 0 && rotary_dim <= rot && rotary_dim % 2 == 0, "latent_prepare: rotary_dim %d does not fit %d rotated features", rotary_dim, rot);
     const int width = q_rank + rank + rot;
     TI_REQUIRE(width * 4 <= 48 * 1024, "latent_prepare: latents of %d features do not fit shared memory", width);
     if (num_tokens == 0) return 0;
-    LaRotation r{inv_freq, table, table_positions, interleaved, rotary_dim};
+    LaRotation r{inv_freq, table, table_positions, interleaved, rotary_dim, rot_factor};
     const size_t smem = (size_t)width * 4;
     if (dtype == TI_F32)
         ti_launch(latent_prepare_kernel<float>, num_tokens, LP_THREADS, smem, stream, (float*)q_latent, (float*)cache, down, ld,
@@ -110,10 +116,10 @@ TI_API int ti_latent_prepare(void* q_latent, void* cache, const float* down, int
 }
 
 // ------------------------------------------------------------------ query rotation
-// q [T, H, plain + rot] in the compute dtype -> rows[t][h][rank .. rank + rot) float32 (the first `rank` features
+// q [T, H, plain + rot] (rows of ld_q elements) in the compute dtype -> rows[t][h][rank .. rank + rot) float32 (the first `rank` features
 // of a row are written by the batched product with the key maps).
 template <typename T>
-__global__ void latent_query_kernel(float* __restrict__ rows, const T* __restrict__ q, int heads, int plain, int rot, int rank,
+__global__ void latent_query_kernel(float* __restrict__ rows, const T* __restrict__ q, int ld_q, int heads, int plain, int rot, int rank,
                                     LaRotation rotation, const int* __restrict__ positions) {
     extern __shared__ float part[];
     ti_grid_launch_dependents();
@@ -123,7 +129,7 @@ __global__ void latent_query_kernel(float* __restrict__ rows, const T* __restric
     const int n = heads * rot;
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
         const int h = i / rot, f = i % rot;
-        part[i] = to_f32(q[((size_t)t * heads + h) * (plain + rot) + plain + f]);
+        part[i] = to_f32(q[(size_t)t * ld_q + (size_t)h * (plain + rot) + plain + f]);
     }
     __syncthreads();
     const bool in_table = rotation.table == nullptr || (pos >= 0 && pos < rotation.table_positions);
@@ -133,19 +139,19 @@ __global__ void latent_query_kernel(float* __restrict__ rows, const T* __restric
     }
 }
 
-TI_API int ti_latent_query(float* rows, const void* q, int num_tokens, int heads, int plain, int rot, int rank,
+TI_API int ti_latent_query(float* rows, const void* q, int ld_q, int num_tokens, int heads, int plain, int rot, int rank,
                            const float* inv_freq, const float* table, int table_positions, int interleaved, int rotary_dim,
-                           const int* positions, int dtype, cudaStream_t stream) {
-    TI_REQUIRE(num_tokens >= 0 && heads > 0 && plain >= 0 && rot >= 0 && rank > 0, "latent_query: bad sizes");
+                           float rot_factor, const int* positions, int dtype, cudaStream_t stream) {
+    TI_REQUIRE(num_tokens >= 0 && heads > 0 && plain >= 0 && rot >= 0 && rank > 0 && ld_q >= heads * (plain + rot), "latent_query: bad sizes");
     TI_REQUIRE(rotary_dim >= 0 && rotary_dim <= rot && rotary_dim % 2 == 0, "latent_query: rotary_dim %d does not fit %d rotated features", rotary_dim, rot);
     TI_REQUIRE(heads * rot * 4 <= 48 * 1024, "latent_query: %d rotated features do not fit shared memory", heads * rot);
     if (num_tokens == 0 || rot == 0) return 0;
-    LaRotation r{inv_freq, table, table_positions, interleaved, rotary_dim};
+    LaRotation r{inv_freq, table, table_positions, interleaved, rotary_dim, rot_factor};
     const size_t smem = (size_t)heads * rot * 4;
     if (dtype == TI_F32)
-        ti_launch(latent_query_kernel<float>, num_tokens, 128, smem, stream, rows, (const float*)q, heads, plain, rot, rank, r, positions);
+        ti_launch(latent_query_kernel<float>, num_tokens, 128, smem, stream, rows, (const float*)q, ld_q, heads, plain, rot, rank, r, positions);
     else if (dtype == TI_BF16)
-        ti_launch(latent_query_kernel<__nv_bfloat16>, num_tokens, 128, smem, stream, rows, (const __nv_bfloat16*)q, heads, plain, rot, rank, r, positions);
+        ti_launch(latent_query_kernel<__nv_bfloat16>, num_tokens, 128, smem, stream, rows, (const __nv_bfloat16*)q, ld_q, heads, plain, rot, rank, r, positions);
     else TI_REQUIRE(false, "latent_query: unknown dtype %d", dtype);
     TI_CHECK_LAUNCH("latent_query");
     return 0;

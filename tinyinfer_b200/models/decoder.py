@@ -33,7 +33,8 @@ class DecoderModel:
     # ------------------------------------------------------------------ tensors
     def _part_prefixes(self, i: int):
         n = self.spec.names
-        base = n.layer.format(i=i)
+        number = self.spec.layers[i].index
+        base = n.layer.format(i=i if number is None else number)
         block = self.blocks[i]
         parts = [(base + n.mixer, block.mixer), (base + n.feed_forward, block.feed_forward),
                  (base + n.mixer_norm, block.mixer_norm),
@@ -126,3 +127,30 @@ class DecoderModel:
         block's output."""
         h = self.final_norm.forward_rows(x, step.logit_rows)
         return ops.linear(h, self.head, out_float32=True)
+
+
+class StreamDecoderModel(DecoderModel):
+    """The frame of the decoders whose blocks are 'multi_stream' blocks around ONE float32 residual stream: the
+    embedding times a constant goes into the stream; at the end the last sublayer's update, the final norm and the
+    choice of the wanted rows are one kernel, then the head and, if asked for, a smooth cap c * tanh(z / c) on the
+    logits. What travels between the blocks is the pair (stream [1, T, width], update still to be applied)."""
+
+    def __init__(self, spec: ModelSpec, dtype, device, *, embedding_scale: float = 1.0,
+                 logit_softcap: Optional[float] = None):
+        super().__init__(spec, dtype, device)
+        self.embedding_scale = float(embedding_scale)
+        self.logit_softcap = logit_softcap
+        self._one = None
+
+    def embed(self, step):
+        return ops.streams_embed(step.token_ids, self.embedding, 1, self.embedding_scale), None
+
+    def logits(self, x, step):
+        stream, pending = x
+        if self._one is None:
+            self._one = torch.ones(1, dtype=torch.float32, device=self.device)
+        rms = self.final_norm.as_rms()
+        # the last sublayer's update and the final norm, for the wanted rows only
+        h = ops.streams_step(stream, pending, self._one, rms[0], rms[1], self.dtype, rows=step.logit_rows)
+        z = ops.linear(h, self.head, out_float32=True)
+        return ops.soft_cap_(z, self.logit_softcap) if self.logit_softcap else z

@@ -6,33 +6,16 @@ function are the generic decoder's; this class only has the frame: an embedding 
 stream, and at the end the final norm on the wanted rows, an untied head and a smooth cap on the logits."""
 from __future__ import annotations
 
-import torch
-
-from .. import ops
 from ..config.registry import register_architecture
 from ..config.sinulix import NAME, SinulixConfig
-from .decoder import DecoderModel
+from .decoder import StreamDecoderModel
 
 
-class SinulixForCausalLM(DecoderModel):
+class SinulixForCausalLM(StreamDecoderModel):
     def __init__(self, config: SinulixConfig, dtype, device):
-        super().__init__(config.model_spec(), dtype, device)
+        super().__init__(config.model_spec(), dtype, device, embedding_scale=config.embedding_scale,
+                         logit_softcap=config.logit_softcap)
         self.config = config
-        self._one = None
-
-    def embed(self, step):
-        """(the float32 stream [1, T, width], the update still to be applied to it: none yet)."""
-        return ops.streams_embed(step.token_ids, self.embedding, 1, self.config.embedding_scale), None
-
-    def logits(self, x, step):
-        stream, pending = x
-        if self._one is None:
-            self._one = torch.ones(1, dtype=torch.float32, device=self.device)
-        rms = self.final_norm.as_rms()
-        # the last sublayer's update and the final norm, for the wanted rows only
-        h = ops.streams_step(stream, pending, self._one, rms[0], rms[1], self.dtype, rows=step.logit_rows)
-        z = ops.linear(h, self.head, out_float32=True)
-        return ops.soft_cap_(z, self.config.logit_softcap) if self.config.logit_softcap else z
 
 
 def _layers(pattern: str, attention: dict, retention: dict, delta: dict, dense: dict, moe: dict):

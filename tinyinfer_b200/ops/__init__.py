@@ -53,12 +53,12 @@ _SIGNATURES = {
         "ti_rmsnorm_rows32": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_void_p],
         "ti_relu_squared": [c_void_p, c_void_p, c_ll, c_int, c_void_p],
         "ti_gemm_batched": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_ll, c_ll, c_ll, c_ll,
-                            c_ll, c_ll, c_ll, c_int, c_int, c_int, c_void_p],
+                            c_ll, c_ll, c_ll, c_int, c_int, c_void_p, c_ll, c_ll, c_int, c_void_p],
         "ti_latent_prepare": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_float, c_int, c_int, c_int,
-                              c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                              c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                               c_int, c_void_p, c_int, c_void_p],
-        "ti_latent_query": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
-                            c_void_p, c_int, c_void_p],
+        "ti_latent_query": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
+                            c_float, c_void_p, c_int, c_void_p],
         "ti_latent_attend": [c_void_p, c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                              c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_int, c_void_p],
         "ti_latent_merge": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
@@ -74,13 +74,14 @@ _SIGNATURES = {
     # routed experts
     "experts": {
         "ti_moe_route": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                         c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                         c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                          c_void_p],
         "ti_moe_tile_rows": [],
         "ti_moe_gemm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                         c_void_p],
         "ti_moe_wide_tiles_ok": [c_int, c_int],
-        "ti_moe_gather": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+        "ti_moe_gather": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p],
+        "ti_moe_silu_glu": [c_void_p, c_void_p, c_ll, c_int, c_int, c_void_p],
         "ti_moe_combine_norm_add": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                     c_int, c_float, c_int, c_void_p],
         "ti_moe_clamped_glu": [c_void_p, c_void_p, c_ll, c_int, c_float, c_float, c_int, c_void_p],
@@ -93,13 +94,13 @@ _SIGNATURES = {
         "ti_streams_embed": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
         "ti_soft_cap": [c_void_p, c_ll, c_float, c_void_p],
         "ti_head_rotation": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_float, c_void_p,
-                             c_void_p, c_int, c_int, c_int, c_float, c_float, c_void_p, c_void_p, c_void_p, c_int, c_int,
-                             c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p],
+                             c_void_p, c_int, c_int, c_int, c_float, c_float, c_float, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                             c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_int, c_void_p],
         "ti_delta_scan": [c_void_p, c_void_p, c_ll, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int,
                           c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_float, c_float, c_void_p,
                           c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_ll, c_int, c_void_p],
         "ti_streams_step": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int,
-                            c_int, c_int, c_int, c_int, c_int, c_void_p],
+                            c_int, c_int, c_int, c_int, c_int, c_void_p, c_float, c_void_p],
         "ti_gelu": [c_void_p, c_void_p, c_ll, c_int, c_int, c_void_p],
         "ti_scale": [c_void_p, c_ll, c_float, c_void_p],
         "ti_short_conv": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -111,7 +112,7 @@ _SIGNATURES = {
                                c_int, c_int, c_void_p, c_int, c_void_p],
         "ti_attention_rows": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                               c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_float, c_void_p, c_void_p, c_int, c_int,
-                              c_float, c_void_p, c_int, c_void_p],
+                              c_float, c_float, c_void_p, c_int, c_void_p],
         "ti_linear_scan": [c_void_p, c_void_p, c_ll, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int,
                            c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p, c_float, c_void_p,
                            c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_ll, c_void_p, c_int, c_void_p],
@@ -476,10 +477,11 @@ class Rotation:
     rotated in pairs, (j, j + rotary_dim / 2) or, ``interleaved``, (2j, 2j + 1), pair j of position p by
     the angle p * inv_freq[j] (``inv_freq`` float32 [rotary_dim / 2]) or by the angle whose cosine and
     sine stand in ``cos_sin`` (float32 [positions, rotary_dim]: a row holds the rotary_dim / 2 cosines,
-    then the sines; any encoding whose angles depend on the position alone). Exactly one of the two."""
+    then the sines; any encoding whose angles depend on the position alone). Exactly one of the two.
+    ``factor`` multiplies every cosine and sine (an encoding that lengthens what it turns)."""
 
     def __init__(self, rotary_dim: int, inv_freq: Optional[torch.Tensor] = None,
-                 cos_sin: Optional[torch.Tensor] = None, interleaved: bool = False):
+                 cos_sin: Optional[torch.Tensor] = None, interleaved: bool = False, factor: float = 1.0):
         if (inv_freq is None) == (cos_sin is None):
             raise KernelError("a rotation needs inverse frequencies or a table of cosines and sines, one of them")
         if rotary_dim <= 0 or rotary_dim % 2:
@@ -490,6 +492,7 @@ class Rotation:
         elif cos_sin.dtype != torch.float32 or cos_sin.dim() != 2 or cos_sin.shape[1] != rotary_dim:
             raise KernelError("cos_sin must be float32 [positions, rotary_dim]")
         self.rotary_dim, self.inv_freq, self.cos_sin, self.interleaved = rotary_dim, inv_freq, cos_sin, bool(interleaved)
+        self.factor = float(factor)
 
 
 def qk_norm_rope_append(qkv: torch.Tensor, *, num_heads: int, num_kv_heads: int, head_dim: int,
@@ -521,6 +524,8 @@ def qk_norm_rope_append(qkv: torch.Tensor, *, num_heads: int, num_kv_heads: int,
     if rotation is not None:
         if rotation.rotary_dim > head_dim:
             raise KernelError(f"rotary_dim {rotation.rotary_dim} exceeds head_dim {head_dim}")
+        if rotation.factor != 1.0:
+            raise KernelError("qk_norm_rope_append turns without a factor; head_rotation takes one")
         _check(rotation.inv_freq if rotation.inv_freq is not None else rotation.cos_sin, "the rotation's tensor")
     page_size = num_pages = 1
     if kv_cache is not None:
@@ -637,13 +642,13 @@ def paged_attention(q: torch.Tensor, kv_cache: torch.Tensor, *, positions: torch
                     window: Optional[int] = None, step=None,
                     status: Optional[torch.Tensor] = None, sink: Optional[float] = None,
                     out_scale: float = 1.0, head_sinks: Optional[torch.Tensor] = None,
-                    gate: Optional[torch.Tensor] = None, gate_offset: int = 0) -> torch.Tensor:
+                    gate: Optional[torch.Tensor] = None, gate_offset: int = 0, softcap: float = 0.0) -> torch.Tensor:
     """Causal attention of q [T, Hq, D] over the pages of each token's own request.
     Token t sees keys max(0, pos - window + 1) .. pos of request ``token_seq[t]``.
     ``sink``: a logit whose exponential joins every softmax denominator without a value (0.0 adds one to the sum
     of exp(score)); ``head_sinks`` float32 [Hq]: such a logit per query head instead; ``gate`` [T, cols] of q's dtype:
     the output of (token, head) is multiplied by sigmoid(gate[token, gate_offset + head]); ``out_scale``: a factor on
-    the output before its rounding.
+    the output before its rounding; ``softcap`` > 0: a score s becomes softcap * tanh(s / softcap) before the softmax.
     Returns [T, Hq * D]. ``step`` (the StepContext of the batch) carries the split of the batch
     into decoded tokens and prompt portions; without it the split is derived here (a device read)."""
     _check(q, "q", None, 3)
@@ -661,13 +666,13 @@ def paged_attention(q: torch.Tensor, kv_cache: torch.Tensor, *, positions: torch
     has_sink, sink_v = int(sink is not None), float(sink or 0.0)
     _check_head_extras(q, head_sinks, gate, gate_offset)
     extras = (_ptr(head_sinks), _ptr(gate), gate.shape[1] if gate is not None else 0, int(gate_offset))
-    if not attention_tensor_cores_ok(q, kv_cache):
-        if q.dtype == torch.bfloat16:
+    if softcap or not attention_tensor_cores_ok(q, kv_cache):
+        if q.dtype == torch.bfloat16 and not attention_tensor_cores_ok(q, kv_cache):
             _warn_generic_attention(hq, hkv, d, page_size)
-        if has_sink or out_scale != 1.0 or head_sinks is not None or gate is not None:
+        if softcap or has_sink or out_scale != 1.0 or head_sinks is not None or gate is not None:
             return attention_rows(q, kv_cache, v_dim=d, positions=positions, token_seq=token_seq, block_table=block_table,
                                   scale=scale, sink=sink, window=window, out_scale=out_scale, status=status,
-                                  head_sinks=head_sinks, gate=gate, gate_offset=gate_offset)
+                                  head_sinks=head_sinks, gate=gate, gate_offset=gate_offset, softcap=softcap)
         _run("core", "ti_attention_generic", out.data_ptr(), q.data_ptr(), kv_cache.data_ptr(),
              positions.data_ptr(), token_seq.data_ptr(), block_table.data_ptr(), block_table.shape[1],
              t, hq, hkv, d, page_size, num_pages, float(scale), int(window or 0), _ptr(status),
@@ -787,8 +792,10 @@ def relu_squared(x: torch.Tensor) -> torch.Tensor:
 
 def batched_linear(x: torch.Tensor, w: torch.Tensor, *, x_offset: int = 0, x_batch_stride: int, k: int,
                    out: Optional[torch.Tensor] = None, out_offset: int = 0, out_batch_stride: Optional[int] = None,
-                   bias: Optional[torch.Tensor] = None, sigmoid: bool = False, out_float32: bool = False) -> torch.Tensor:
+                   bias: Optional[torch.Tensor] = None, sigmoid: bool = False, out_float32: bool = False,
+                   gate: Optional[torch.Tensor] = None, gate_offset: int = 0) -> torch.Tensor:
     """For every batch b of ``w`` [B, N, K]: out[:, b-th piece] = act(x[:, b-th piece] . w[b]^T + bias[b]).
+    ``gate`` [M, cols] of x's dtype: batch b's result is also multiplied by sigmoid(gate[:, gate_offset + b * N + n]).
     ``x`` [M, row] holds the batches side by side in each row: piece b starts at column
     ``x_offset + b * x_batch_stride`` and has ``k`` columns; likewise ``out`` [M, row_out] (made here as
     [M, B * N] if not given) with ``out_offset`` and ``out_batch_stride`` (default N). float32 accumulation."""
@@ -814,31 +821,39 @@ def batched_linear(x: torch.Tensor, w: torch.Tensor, *, x_offset: int = 0, x_bat
         _check(bias, "bias", torch.float32, 2)
         if tuple(bias.shape) != (batch, n):
             raise KernelError("batched_linear: bias must be [B, N]")
+    if gate is not None:
+        _check(gate, "gate", x.dtype, 2)
+        if gate.shape[0] != m or gate_offset < 0 or gate_offset + batch * n > gate.shape[1]:
+            raise KernelError("batched_linear: the gate holds one column per output for every row")
     isz_x, isz_o = x.element_size(), out.element_size()
     _run("latent", "ti_gemm_batched", out.data_ptr() + out_offset * isz_o, x.data_ptr() + x_offset * isz_x, w.data_ptr(),
          _ptr(bias), batch, m, n, k, x.shape[1], x_batch_stride, k, n * k, out.shape[1], out_batch_stride, n,
-         int(sigmoid), int(out.dtype == torch.float32 and x.dtype != torch.float32), _dtype_code(x), _stream())
+         int(sigmoid), int(out.dtype == torch.float32 and x.dtype != torch.float32),
+         gate.data_ptr() + gate_offset * isz_x if gate is not None else None, gate.shape[1] if gate is not None else 0, n,
+         _dtype_code(x), _stream())
     return out
 
 
 # ---------------------------------------------------------------------- attention over a cached latent
 def _rotation_args(rot: Optional[Rotation]):
     if rot is None:
-        return None, None, 0, 0, 0
+        return None, None, 0, 0, 0, 1.0
     _check(rot.inv_freq if rot.inv_freq is not None else rot.cos_sin, "the rotation's tensor")
     return (_ptr(rot.inv_freq), _ptr(rot.cos_sin), rot.cos_sin.shape[0] if rot.cos_sin is not None else 0,
-            int(rot.interleaved), rot.rotary_dim)
+            int(rot.interleaved), rot.rotary_dim, float(rot.factor))
 
 
-def latent_prepare(down: torch.Tensor, *, q_rank: int, rank: int, rot: int, q_norm_weight: torch.Tensor,
+def latent_prepare(down: torch.Tensor, *, q_rank: int, rank: int, rot: int, q_norm_weight: Optional[torch.Tensor],
                    kv_norm_weight: Optional[torch.Tensor], eps: float, rotation: Optional[Rotation],
                    positions: torch.Tensor, token_seq: torch.Tensor, cache: Optional[torch.Tensor],
                    block_table: torch.Tensor, dtype: torch.dtype, status: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``down`` float32 [T, q_rank (+ rank + rot)]: a token's down projections [query latent | kv latent | keys to
     rotate]. Returns the normed query latent [T, q_rank] in ``dtype`` and, if ``cache`` ([1, pages, 1, page,
-    rank + rot], ``dtype``) is given, writes the token's row [normed kv latent | rotated keys] there."""
+    rank + rot], ``dtype``) is given, writes the token's row [normed kv latent | rotated keys] there. ``q_rank`` 0: the
+    queries have no latent of their own (nothing is returned)."""
     _check(down, "down", torch.float32, 2)
-    _check(q_norm_weight, "q_norm_weight", torch.float32, 1)
+    if q_rank:
+        _check(q_norm_weight, "q_norm_weight", torch.float32, 1)
     _check(positions, "positions", torch.int32, 1)
     _check(token_seq, "token_seq", torch.int32, 1)
     t = down.shape[0]
@@ -854,24 +869,24 @@ def latent_prepare(down: torch.Tensor, *, q_rank: int, rank: int, rot: int, q_no
         if cache.shape[0] != 1 or cache.shape[2] != 1 or cache.shape[4] != rank + rot:
             raise KernelError(f"latent cache shape {tuple(cache.shape)} is not [1, pages, 1, page, {rank + rot}]")
         num_pages, page_size, max_blocks = cache.shape[1], cache.shape[3], block_table.shape[1]
-    out = torch.empty((t, q_rank), dtype=dtype, device=down.device)
-    _run("latent", "ti_latent_prepare", out.data_ptr(), _ptr(cache), down.data_ptr(), down.shape[1],
-         q_norm_weight.data_ptr(), _ptr(kv_norm_weight), float(eps), q_rank, rank, rot, *_rotation_args(rotation),
+    out = torch.empty((t, q_rank), dtype=dtype, device=down.device) if q_rank else None
+    _run("latent", "ti_latent_prepare", _ptr(out), _ptr(cache), down.data_ptr(), down.shape[1],
+         _ptr(q_norm_weight) if q_rank else None, _ptr(kv_norm_weight), float(eps), q_rank, rank, rot, *_rotation_args(rotation),
          positions.data_ptr(), token_seq.data_ptr(), _ptr(block_table) if cache is not None else None, max_blocks, t,
-         page_size, num_pages, _ptr(status), _dtype_code(out), _stream())
+         page_size, num_pages, _ptr(status), 0 if dtype == torch.float32 else 1, _stream())
     return out
 
 
 def latent_query_rotate(rows: torch.Tensor, q: torch.Tensor, *, heads: int, plain: int, rot: int, rank: int,
                         rotation: Optional[Rotation], positions: torch.Tensor) -> None:
-    """Writes the rotated last ``rot`` features of every head of ``q`` [T, heads * (plain + rot)] into
+    """Writes the rotated last ``rot`` features of every head of ``q`` [T, heads * (plain + rot) (+ columns not read)] into
     ``rows`` float32 [T, heads * (rank + rot)], behind each head's first ``rank`` features."""
     _check(rows, "rows", torch.float32, 2)
     _check(q, "q", None, 2)
     _check(positions, "positions", torch.int32, 1)
-    if q.shape[1] != heads * (plain + rot) or rows.shape[1] != heads * (rank + rot) or rows.shape[0] != q.shape[0]:
+    if q.shape[1] < heads * (plain + rot) or rows.shape[1] != heads * (rank + rot) or rows.shape[0] != q.shape[0]:
         raise KernelError("latent_query_rotate: widths do not match the head sizes")
-    _run("latent", "ti_latent_query", rows.data_ptr(), q.data_ptr(), q.shape[0], heads, plain, rot, rank,
+    _run("latent", "ti_latent_query", rows.data_ptr(), q.data_ptr(), q.shape[1], q.shape[0], heads, plain, rot, rank,
          *_rotation_args(rotation), positions.data_ptr(), _dtype_code(q), _stream())
 
 
@@ -1001,13 +1016,14 @@ class ExpertRouting:
 
 def route_experts(x32: torch.Tensor, w_router: torch.Tensor, top: int, weight_eps: float,
                   wide_tiles: bool = False, tile_rows: int = 0, *, correction: Optional[torch.Tensor] = None,
-                  renormalize: bool = True, real_experts: Optional[int] = None) -> ExpertRouting:
+                  renormalize: bool = True, real_experts: Optional[int] = None, scoring: str = "softmax") -> ExpertRouting:
     """Router of a mixture of experts: float32 logits from the rows ``x32`` [T, H] (float32, or the router's dtype)
     and ``w_router`` [E, H], softmax over all experts, the ``top`` largest (first index on ties), weights = their
     scores over their sum (+ ``weight_eps``). ``correction`` float32 [E]: the choice goes by score + correction, the
     weights stay the plain scores; ``renormalize`` False: the weights are the scores themselves; ``real_experts``:
     only the first so many router outputs are experts with weights, the rest stand for identity experts (rows, but
-    no tiles in the plan). ``wide_tiles``: the row tiles of the plan hold 64 rows instead of 32 (for steps that bring
+    no tiles in the plan). ``scoring`` 'sigmoid': an expert's score is the sigmoid of its own logit instead of the
+    softmax over all. ``wide_tiles``: the row tiles of the plan hold 64 rows instead of 32 (for steps that bring
     an expert many rows; only the tensor-core grouped product takes them, see ``expert_tiles_may_be_wide``);
     ``tile_rows``: any other height the caller has settled with the grouped product (``expert_tile_rows``)."""
     _check(x32, "x32", None, 2)
@@ -1023,6 +1039,8 @@ def route_experts(x32: torch.Tensor, w_router: torch.Tensor, top: int, weight_ep
         if correction.shape[0] != experts:
             raise KernelError("route_experts: one correction per router output")
     real = experts if real_experts is None else int(real_experts)
+    if scoring not in ("softmax", "sigmoid"):
+        raise KernelError(f"route_experts: unknown scoring {scoring!r}")
     dev = x32.device
     tile_rows = tile_rows or (64 if wide_tiles else int(_fn("experts", "ti_moe_tile_rows")()))
     max_tiles = (t * top + tile_rows - 1) // tile_rows + experts
@@ -1037,7 +1055,8 @@ def route_experts(x32: torch.Tensor, w_router: torch.Tensor, top: int, weight_ep
     _run("experts", "ti_moe_route", chosen.data_ptr(), weight.data_ptr(), rank.data_ptr(), counts.data_ptr(),
          starts.data_ptr(), tiles.data_ptr(), num_tiles.data_ptr(), slot_of.data_ptr(), token_of.data_ptr(),
          x32.data_ptr(), w_router.data_ptr(), t, hidden, experts, top, float(weight_eps), _ptr(correction),
-         int(renormalize), real, tile_rows, max_tiles, _dtype_code(x32), _dtype_code(w_router), _stream())
+         int(renormalize), real, tile_rows, max_tiles, int(scoring == "sigmoid"), _dtype_code(x32), _dtype_code(w_router),
+         _stream())
     return ExpertRouting(chosen.view(t, top), weight, slot_of.view(t, top), token_of, tiles.view(max_tiles, 3),
                          num_tiles, max_tiles, counts, tile_rows)
 
@@ -1064,11 +1083,13 @@ def expert_tile_rows(x: torch.Tensor, num_experts: int, top: int, *inner_sizes: 
     return int(_fn("experts", "ti_moe_tile_rows")())
 
 
-def expert_linear(x: torch.Tensor, w: torch.Tensor, routing: ExpertRouting, *, up: bool, activation: bool = True) -> torch.Tensor:
+def expert_linear(x: torch.Tensor, w: torch.Tensor, routing: ExpertRouting, *, up: bool, activation: bool = True,
+                  weighted_input: bool = False) -> torch.Tensor:
     """Grouped product over the routing's row tiles with ``w`` [E, N, K]. ``up``: ``x`` [T, K] are the step's
     tokens, gathered per expert; the result [T * top, N] (sorted rows) has passed max(v, 0)^2 (``activation``
     False: it is stored as it is, for an activation that is a kernel of its own). Otherwise ``x``
-    are sorted rows [T * top, K] and the result is float32 [T * top, N]."""
+    are sorted rows [T * top, K] and the result is float32 [T * top, N]. ``weighted_input`` (with ``up``): the row
+    an expert reads is the token's row times the weight of that (token, choice), rounded once."""
     _check(x, "x", None, 2)
     _check(w, "w", x.dtype, 3)
     _, n, k = w.shape
@@ -1077,16 +1098,26 @@ def expert_linear(x: torch.Tensor, w: torch.Tensor, routing: ExpertRouting, *, u
     slots = routing.token_of.shape[0]
     out = torch.empty((slots, n), dtype=x.dtype if up else torch.float32, device=x.device)
     form = (1 if activation else 2) if up else 0
+    if weighted_input and not (up and not activation):
+        raise KernelError("expert_linear: weighted rows enter an up product whose activation is a kernel of its own")
+
+    def gathered(weights: bool) -> torch.Tensor:
+        rows = torch.empty((slots, k), dtype=x.dtype, device=x.device)
+        _run("experts", "ti_moe_gather", rows.data_ptr(), x.data_ptr(), routing.token_of.data_ptr(), slots, k,
+             routing.slot_of.data_ptr() if weights else None, routing.weight.data_ptr() if weights else None,
+             routing.chosen.shape[1], _dtype_code(x), _stream())
+        return rows
+
     if routing.tile_rows == 128:                 # tcgen05: tiled operand copies want the rows in expert order
         rows = x
         if up:
-            rows = torch.empty((slots, k), dtype=x.dtype, device=x.device)
-            _run("experts", "ti_moe_gather", rows.data_ptr(), x.data_ptr(), routing.token_of.data_ptr(), slots, k,
-                 _dtype_code(x), _stream())
+            rows = gathered(weighted_input)
         _run("sm100", "ti_moe_gemm_tcgen05", out.data_ptr(), rows.data_ptr(), w.data_ptr(), routing.tiles.data_ptr(),
              routing.num_tiles.data_ptr(), slots, w.shape[0], n, k, routing.max_tiles, form,
              kernel_status(x.device).data_ptr(), _stream())
         return out
+    if weighted_input:                           # the rows are scaled while they are put in expert order
+        x, form = gathered(True), 3
     _run("experts", "ti_moe_gemm", out.data_ptr(), x.data_ptr(), w.data_ptr(), routing.tiles.data_ptr(),
          routing.num_tiles.data_ptr(), routing.token_of.data_ptr(), n, k, routing.max_tiles, routing.tile_rows, form,
          _dtype_code(x), _stream())
@@ -1125,10 +1156,24 @@ def clamped_glu(gate_up: torch.Tensor, limit: float, alpha: float) -> torch.Tens
     return out
 
 
-def experts_combine(down: torch.Tensor, x: torch.Tensor, routing: ExpertRouting, real_experts: int) -> torch.Tensor:
+def silu_glu(gate_up: torch.Tensor) -> torch.Tensor:
+    """silu(gate) * up on a stored product ``gate_up`` [rows, 2 F] = [gate | up] -> [rows, F]; float32 arithmetic, one
+    rounding."""
+    _check(gate_up, "gate_up", None, 2)
+    rows, two_f = gate_up.shape
+    if two_f % 2:
+        raise KernelError("silu_glu: a row holds a gate half and an up half")
+    out = torch.empty((rows, two_f // 2), dtype=gate_up.dtype, device=gate_up.device)
+    _run("experts", "ti_moe_silu_glu", out.data_ptr(), gate_up.data_ptr(), rows, two_f // 2, _dtype_code(gate_up), _stream())
+    return out
+
+
+def experts_combine(down: torch.Tensor, x: torch.Tensor, routing: ExpertRouting, real_experts: int,
+                    weighted: bool = True) -> torch.Tensor:
     """out[t] = sum_c weight[t, c] * (down[slot_of[t, c]] if chosen[t, c] < real_experts else x[t]) in choice order:
     the weighted sum of the chosen experts' outputs (float32 sorted rows ``down``), an identity expert's output being
-    the token's own row of ``x`` [T, H]. Float32 sums, one rounding to x's dtype."""
+    the token's own row of ``x`` [T, H]. Float32 sums, one rounding to x's dtype. ``weighted`` False: every weight is
+    one (the experts were weighted at their input)."""
     _check(down, "down", torch.float32, 2)
     _check(x, "x", None, 2)
     t, size = x.shape
@@ -1136,8 +1181,8 @@ def experts_combine(down: torch.Tensor, x: torch.Tensor, routing: ExpertRouting,
         raise KernelError("experts_combine: the rows do not fit the routing")
     out = torch.empty_like(x)
     _run("experts", "ti_moe_combine", out.data_ptr(), down.data_ptr(), x.data_ptr(), routing.chosen.data_ptr(),
-         routing.slot_of.data_ptr(), routing.weight.data_ptr(), t, size, routing.chosen.shape[1], int(real_experts),
-         _dtype_code(x), _stream())
+         routing.slot_of.data_ptr(), routing.weight.data_ptr() if weighted else None, t, size, routing.chosen.shape[1],
+         int(real_experts), _dtype_code(x), _stream())
     return out
 
 
@@ -1156,8 +1201,11 @@ class StreamUpdate:
     """What a sublayer leaves for the streams, applied by the next ``streams_step``:
     X[t] <- sum_s mix[s, t] X[s] + out[t] * y (``mix`` float32 [S, S] indexed [from, to], ``out`` float32 [S])."""
 
-    def __init__(self, y: torch.Tensor, mix: torch.Tensor, out: torch.Tensor):
+    def __init__(self, y: torch.Tensor, mix: torch.Tensor, out: torch.Tensor,
+                 norm_weight: Optional[torch.Tensor] = None, norm_eps: float = 0.0):
         self.y, self.mix, self.out = y, mix, out
+        # a norm on the sublayer's OUTPUT: y is replaced by norm_weight * y * rsqrt(mean(y^2) + norm_eps) as it is applied
+        self.norm_weight, self.norm_eps = norm_weight, float(norm_eps)
 
 
 def streams_step(x: torch.Tensor, pending: Optional[StreamUpdate], read_in: Optional[torch.Tensor],
@@ -1176,6 +1224,10 @@ def streams_step(x: torch.Tensor, pending: Optional[StreamUpdate], read_in: Opti
         _check(pending.out, "out", torch.float32, 1)
         if tuple(y.shape) != (t, width) or tuple(pending.mix.shape) != (s, s) or pending.out.shape[0] != s:
             raise KernelError("streams_step: the update does not fit the streams")
+        if pending.norm_weight is not None:
+            _check(pending.norm_weight, "the update's norm weight", torch.float32, 1)
+            if pending.norm_weight.shape[0] != width:
+                raise KernelError("streams_step: the update's norm does not fit the streams")
     h = None
     n = t if rows is None else _check(rows, "rows", torch.int32, 1).shape[0]
     if read_in is not None:
@@ -1186,7 +1238,8 @@ def streams_step(x: torch.Tensor, pending: Optional[StreamUpdate], read_in: Opti
         h = torch.empty((n, width), dtype=out_dtype, device=x.device)
     _run("hybrid", "ti_streams_step", x.data_ptr(), _ptr(y), _ptr(pending.mix) if pending else None,
          _ptr(pending.out) if pending else None, _ptr(read_in), _ptr(norm_weight), float(eps), _ptr(h), _ptr(rows), n, t,
-         width, s, _dtype_code(y) if y is not None else 0, _dtype_code(h) if h is not None else 0, _stream())
+         width, s, _dtype_code(y) if y is not None else 0, _dtype_code(h) if h is not None else 0,
+         _ptr(pending.norm_weight) if pending else None, pending.norm_eps if pending else 0.0, _stream())
     return h
 
 
@@ -1330,12 +1383,13 @@ def attention_rows(q: torch.Tensor, cache: torch.Tensor, *, v_dim: int, position
                    block_table: torch.Tensor, scale: float, sink: Optional[float] = None, window: Optional[int] = None,
                    out_scale: float = 1.0, step=None, status: Optional[torch.Tensor] = None,
                    head_sinks: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None,
-                   gate_offset: int = 0) -> torch.Tensor:
+                   gate_offset: int = 0, softcap: float = 0.0) -> torch.Tensor:
     """Causal attention of q [T, Hq, d] over pages whose rows are [k (d) | v (dv)] (``cache``
     [1, pages, Hkv, page, d + dv]; or planes [2, pages, Hkv, page, d] where d == dv), float32 arithmetic, any sizes. ``sink``: a logit whose exponential joins every softmax denominator without a
     value (0.0: one is added to the sum of exp(score)); ``head_sinks`` float32 [Hq]: such a logit per query head
     instead. ``gate`` [T, cols] of q's dtype: the output of (token, head) is also multiplied by
-    sigmoid(gate[token, gate_offset + head]). Returns [T, Hq * dv], multiplied by ``out_scale`` before its rounding."""
+    sigmoid(gate[token, gate_offset + head]). ``softcap`` > 0: a score s becomes softcap * tanh(s / softcap) before the
+    softmax. Returns [T, Hq * dv], multiplied by ``out_scale`` before its rounding."""
     _check(q, "q", None, 3)
     _check(cache, "cache", q.dtype, 5)
     _check(positions, "positions", torch.int32, 1)
@@ -1351,7 +1405,7 @@ def attention_rows(q: torch.Tensor, cache: torch.Tensor, *, v_dim: int, position
     _run("hybrid", "ti_attention_rows", out.data_ptr(), q.data_ptr(), cache.data_ptr(), positions.data_ptr(),
          token_seq.data_ptr(), block_table.data_ptr(), block_table.shape[1], t, hq, hkv, d, v_dim, page_size, num_pages,
          planes, float(scale), int(window or 0), int(sink is not None), float(sink or 0.0), _ptr(head_sinks), _ptr(gate),
-         gate.shape[1] if gate is not None else 0, int(gate_offset), float(out_scale), _ptr(status),
+         gate.shape[1] if gate is not None else 0, int(gate_offset), float(out_scale), float(softcap or 0.0), _ptr(status),
          _dtype_code(q), _stream())
     return out
 
@@ -1442,13 +1496,15 @@ def head_rotation(rows: torch.Tensor, *, num_heads: int, num_kv_heads: int, head
                   q_norm_weight: Optional[torch.Tensor] = None, k_norm_weight: Optional[torch.Tensor] = None,
                   eps: float = 0.0, rotation: Optional[Rotation] = None, q_scale: float = 1.0, k_scale: float = 1.0,
                   cache: Optional[torch.Tensor] = None, block_table: Optional[torch.Tensor] = None,
-                  out_float32: bool = False, status: Optional[torch.Tensor] = None) -> torch.Tensor:
+                  out_float32: bool = False, status: Optional[torch.Tensor] = None,
+                  norm_after: bool = False) -> torch.Tensor:
     """Per-head RMS norm (plain weights, optional), rotation and constant factors on the query heads, and with
     ``has_kv`` the key heads, that lie in columns [offset, ...) of ``rows`` [T, cols] as [q (Hq d) | k (Hkv d) |
     v (Hkv dv)]; values pass unchanged. With ``cache`` (planes [2, pages, Hkv, page, d] where d == dv, or rows
     [1, pages, Hkv, page, d + dv]) keys and values go to their token's place in the pages and q [T, Hq, d] is
     returned; without one, and with ``has_kv``, the result is the row [q | k | v] (for a recurrent mixer), float32
-    if ``out_float32``. Float32 arithmetic, one rounding."""
+    if ``out_float32``. ``norm_after``: the norm of q and k comes after the rotation, with the weights or, without
+    them, as a plain division by the root mean square. Float32 arithmetic, one rounding."""
     _check(rows, "rows", None, 2)
     _check(positions, "positions", torch.int32, 1)
     _check(token_seq, "token_seq", torch.int32, 1)
@@ -1481,7 +1537,7 @@ def head_rotation(rows: torch.Tensor, *, num_heads: int, num_kv_heads: int, head
              int(offset), _ptr(q_norm_weight), _ptr(k_norm_weight), float(eps), *_rotation_args(rotation), float(q_scale),
              float(k_scale), positions.data_ptr(), token_seq.data_ptr(), _ptr(block_table), max_blocks, t, num_heads,
              num_kv_heads, head_dim, v_dim, int(has_kv), page_size, num_pages, _ptr(status), int(out_float32),
-             _dtype_code(rows), _stream())
+             int(norm_after), _dtype_code(rows), _stream())
     return out if to_row else out.view(t, num_heads, head_dim)
 
 

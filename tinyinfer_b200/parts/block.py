@@ -51,25 +51,41 @@ class MultiStreamBlock(Block):
     (X, update still to be applied): one kernel applies the update a sublayer left and makes the next sublayer's
     input, so a sublayer costs one kernel for all of its residual work. With ``learned_mixing`` the block owns
     ``hc1.{in,out,mix}`` (and ``hc2.*`` if it has a feed-forward); without, all coefficients are 1, which with one
-    stream is the pre-norm residual kept in float32. A block may have no feed-forward."""
+    stream is the pre-norm residual kept in float32. A block may have no feed-forward.
+    ``mixer_out_norm`` / ``feed_forward_out_norm`` of the spec: the sublayer's output passes an RMS norm of its own
+    (a tensor of the block, named from the layer's prefix) before it is added; the same kernel applies it."""
 
     def _coefficients(self):
         return [f"hc{q}" for q in ((1, 2) if self.feed_forward is not None else (1,))]
 
     def tensors(self):
         from .base import TensorSpec
-        if not self.spec.learned_mixing:
-            return {}
-        n = self.spec.streams
         out = {}
+        for norm in self._out_norms().values():
+            out[norm.tensor] = TensorSpec((norm.size,), role="vector32", init="ones_noise")
+        if not self.spec.learned_mixing:
+            return out
+        n = self.spec.streams
         for name in self._coefficients():
             out[f"{name}.in"] = TensorSpec((n,), role="vector32", init="ones_noise")
             out[f"{name}.out"] = TensorSpec((n,), role="vector32", init="ones_noise")
             out[f"{name}.mix"] = TensorSpec((n, n), role="vector32", init="eye_noise")
         return out
 
+    def _out_norms(self):
+        """sublayer -> the NormSpec of the norm on its output, for those that have one."""
+        found = {"hc1": getattr(self.spec, "mixer_out_norm", None)}
+        if self.feed_forward is not None:
+            found["hc2"] = getattr(self.spec, "feed_forward_out_norm", None)
+        for norm in found.values():
+            if norm is not None and (norm.kind != "rmsnorm" or norm.offset):
+                raise ValueError("the norm on a sublayer's output is a plain RMS norm")
+        return {k: v for k, v in found.items() if v is not None}
+
     def load(self, tensors):
-        self.coefficients = {name: tensors[name].contiguous() for name in self.tensors()}
+        out_names = {norm.tensor for norm in self._out_norms().values()}
+        self.coefficients = {name: tensors[name].contiguous() for name in self.tensors() if name not in out_names}
+        self.out_norm_weights = {name: tensors[norm.tensor].contiguous() for name, norm in self._out_norms().items()}
 
     def _coef(self, name: str, device):
         table = getattr(self, "coefficients", None)
@@ -91,12 +107,16 @@ class MultiStreamBlock(Block):
         sublayers = [("hc1", self.mixer_norm, lambda h: self.mixer.forward(h, step, cache))]
         if self.feed_forward is not None:
             sublayers.append(("hc2", self.feed_forward_norm, lambda h: self.feed_forward.forward(h, step)))
+        out_norms = self._out_norms()
         for name, norm, run in sublayers:
             rms = norm.as_rms()
             if rms is None:
                 raise ValueError("the multi-stream arrangement needs RMSNorms")
             h = ops.streams_step(streams, pending, self._coef(f"{name}.in", dev), rms[0], rms[1], dtype)
-            pending = ops.StreamUpdate(run(h), self._coef(f"{name}.mix", dev), self._coef(f"{name}.out", dev))
+            after = out_norms.get(name)
+            pending = ops.StreamUpdate(run(h), self._coef(f"{name}.mix", dev), self._coef(f"{name}.out", dev),
+                                       norm_weight=self.out_norm_weights[name] if after is not None else None,
+                                       norm_eps=after.eps if after is not None else 0.0)
         return (streams, pending), None
 
 

@@ -7,7 +7,10 @@ g = min(W_gate h, limit), u = clamp(W_up h, -limit, limit), down(g * sigmoid(alp
 (the router's last outputs stand for experts whose output is their input; they have no tensors), ``score_correction``
 (a learned number per router output steers the choice, the weights stay the plain scores), ``renormalize`` False (the
 weights are the chosen scores themselves) and ``router_input`` 'input' (the router reads the sublayer's normed input
-instead of the float32 stream).
+instead of the float32 stream), ``activation`` 'silu_glu' (down(silu(W_gate h) * (W_up h))), ``scoring`` 'sigmoid' (an
+expert's score is the sigmoid of its own router logit) and ``weight_input`` (a chosen expert runs on its weight times
+the token's row, expert(w h), and the outputs are summed as they are: the rows are scaled as they are put in expert
+order).
 
 A step's (token, choice) pairs are put in expert order on the device and the experts run as two grouped
 products over row tiles; nothing is read back to the host and no token is ever dropped, so a token's result
@@ -28,15 +31,19 @@ class Experts(FeedForward):
 
     def __init__(self, spec, dtype, device):
         super().__init__(spec, dtype, device)
-        if spec.activation not in ("relu_squared", "clamped_glu"):
-            raise ValueError(f"activation {spec.activation!r} is not supported (relu_squared, clamped_glu)")
+        if spec.activation not in ("relu_squared", "clamped_glu", "silu_glu"):
+            raise ValueError(f"activation {spec.activation!r} is not supported (relu_squared, clamped_glu, silu_glu)")
+        if spec.scoring not in ("softmax", "sigmoid"):
+            raise ValueError(f"scoring {spec.scoring!r} is not supported (softmax, sigmoid)")
+        if spec.weight_input and (spec.activation == "relu_squared" or spec.identity_experts or spec.shared_size):
+            raise ValueError("experts weighted at their input are gated ones, without identity or shared experts")
         if spec.activation == "clamped_glu" and not spec.glu_limit > 0:
             raise ValueError("clamped_glu needs a positive limit")
         if spec.identity_experts < 0 or spec.top > spec.num_experts + spec.identity_experts:
             raise ValueError("top exceeds the number of router outputs")
         if spec.shared_size and spec.activation != "relu_squared":
             raise ValueError("a shared expert is built with the relu_squared activation only")
-        self.glu = spec.activation == "clamped_glu"
+        self.glu = spec.activation in ("clamped_glu", "silu_glu")
         self.w_router = self.w_up = self.w_down = self.w_shared_up = self.w_shared_down = self.correction = None
 
     def tensors(self):
@@ -76,10 +83,12 @@ class Experts(FeedForward):
         # the more rows an expert gets, the taller the row tiles its grouped products are planned with
         routing = ops.route_experts(x32, self.w_router, s.top, s.weight_eps,
                                     tile_rows=ops.expert_tile_rows(x, s.num_experts, s.top, s.expert_size),
-                                    correction=self.correction, renormalize=s.renormalize, real_experts=s.num_experts)
+                                    correction=self.correction, renormalize=s.renormalize, real_experts=s.num_experts,
+                                    scoring=s.scoring)
         if self.glu:
-            hidden = ops.clamped_glu(ops.expert_linear(x, self.w_up, routing, up=True, activation=False),
-                                     s.glu_limit, s.glu_alpha)
+            gate_up = ops.expert_linear(x, self.w_up, routing, up=True, activation=False, weighted_input=s.weight_input)
+            hidden = (ops.silu_glu(gate_up) if s.activation == "silu_glu"
+                      else ops.clamped_glu(gate_up, s.glu_limit, s.glu_alpha))
         else:
             hidden = ops.expert_linear(x, self.w_up, routing, up=True)
         down = ops.expert_linear(hidden, self.w_down, routing, up=False)
@@ -94,8 +103,9 @@ class Experts(FeedForward):
         rms = norm.as_rms()
         if rms is None:
             raise ValueError("the experts' fused output needs an RMSNorm behind them")
-        if self.spec.identity_experts:
-            raise ValueError("identity experts are not built into the fused output of this arrangement")
+        if self.spec.identity_experts or self.spec.weight_input:
+            raise ValueError("identity experts and experts weighted at their input are not built into the fused output "
+                             "of this arrangement")
         routing, down, shared = self._experts(x if self.spec.router_input == "input" else x32, x)
         return ops.experts_combine_norm_add(x32, down, shared, routing, rms[0], rms[1], self.dtype)
 
@@ -106,7 +116,7 @@ class Experts(FeedForward):
         if s.identity_experts and s.router_input != "input":
             raise ValueError("identity experts pass the sublayer's input on, which is also what the router must read")
         routing, down, shared = self._experts(x if s.router_input == "input" or x.dtype == torch.float32 else x.float(), x)
-        out = ops.experts_combine(down, x, routing, s.num_experts)
+        out = ops.experts_combine(down, x, routing, s.num_experts, weighted=not s.weight_input)
         if shared is not None:
             out = ops.add(out, shared)
         return out
