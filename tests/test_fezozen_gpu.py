@@ -1,0 +1,677 @@
+"""The Fezozen design in the engine against its plain statement (tests/plain_fezozen.py): the new and the extended
+kernels alone, each mechanism alone in a model, then whole models in every way of cutting the work (whole prompts, a
+decoded tail, portions down to two tokens, mixed batches with pages used again), keys just inside and just outside a
+window, keys far back that carry the result, the first tokens, long decoding through captured graphs, and greedy
+generation through the entry point and its scheduler. Cache pages are poisoned with NaN so that a read outside a
+request's own rows shows."""
+import copy
+import random
+
+import numpy as np
+import pytest
+import torch
+
+import fezozen_helpers as fh
+import helpers
+import plain_fezozen as plain
+
+pytestmark = pytest.mark.gpu
+
+TOL = {"float32": 5e-5, "bfloat16": 4e-2}     # relative to the largest |logit| of the plain statement
+LENGTHS = [1, 7, 33, 90, 61, 47, 2, 70, 18, 120, 64, 65, 3]
+
+
+def row_errors(got, want):
+    scale = max(float(np.abs(w).max()) for w in want.values())
+    return np.array([float(np.abs(got[r][p].astype(np.float64) - want[r][p]).max()) / scale
+                     for r in sorted(got) for p in sorted(got[r])])
+
+
+def agrees(got, want, dtype):
+    """float32: every row within the tolerance; this is what judges the cache, the windows and the batching.
+    bfloat16: activations rounded to 8 bits through several layers leave a few rows further off than the typical row,
+    and where two sigmoid scores of a router lie within a thousandth of each other the rounding now and then chooses
+    the other expert, which replaces that token's whole feed-forward output (with one expert a token, all of it). So
+    nearly all rows must be within the tolerance, the typical row well within it, and few far outside (a token whose
+    expert changed also leaves other keys and values to the tokens behind it)."""
+    err = row_errors(got, want)
+    if not np.isfinite(err).all():
+        return False
+    if dtype == "float32":
+        return bool(err.max() <= TOL[dtype])
+    return bool((err > TOL[dtype]).mean() <= 0.03 and np.median(err) <= TOL[dtype] / 3 and (err > 4 * TOL[dtype]).mean() <= 0.03)
+
+
+def run(folder, dtype, steps, page, **kw):
+    from tinyinfer_b200.engine.replay import TraceSession
+    session = TraceSession(folder, dtype, helpers.peak_tokens(steps, max(64, page)), page_size=page, poison_cache=True, **kw)
+    got = helpers.collect(session, steps)
+    session.runner.check_status()
+    session.runner.manager.check_consistency()
+    return got, session
+
+
+# ------------------------------------------------------------------ the kernels alone
+@pytest.mark.parametrize("hq,hkv,d,dv,rot,scaled,after", [(6, 2, 20, 12, 12, True, False), (3, 3, 16, 16, 16, False, True),
+                                                          (4, 1, 8, 24, 0, False, True), (8, 8, 128, 128, 64, True, True),
+                                                          (2, 1, 40, 8, 6, True, True)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_head_rotation_with_neighbouring_pairs_a_blend_and_a_late_norm(hq, hkv, d, dv, rot, scaled, after, dtype):
+    """Pairs (2j, 2j + 1), frequencies blended for long contexts with their factor on cosines and sines, and the
+    division by the root mean square AFTER the rotation (which the factor makes differ from a division before it)."""
+    from tinyinfer_b200 import ops
+    from tinyinfer_b200.config.specs import FrequencyBlend, PositionSpec
+    from tinyinfer_b200.parts.base import build_position
+    gen = torch.Generator().manual_seed(hq * d + rot)
+    T, off = 11, 3
+    rows = torch.randn(T, off + hq * d + hkv * (d + dv) + 2, generator=gen).to(dtype)
+    pos = torch.tensor([0, 1, 2, 500, 501, 7, 100000, 3, 64, 65, 4095], dtype=torch.int32)
+    r = fh.rot(777.0, rot, fh.scaling(5.0, 40, 6.0, 0.5) if scaled else None)
+    blend = FrequencyBlend(5.0, 40, 6.0, 0.5) if scaled else None
+    spec = PositionSpec(kind="rope", theta=777.0, rotary_dim=rot, exact_frequencies=True, interleaved=True, blend=blend) \
+        if rot else PositionSpec(kind="none")
+    rotation = build_position(spec, dtype, "cuda").rotation()
+    got = ops.head_rotation(rows.cuda(), num_heads=hq, num_kv_heads=hkv, head_dim=d, v_dim=dv, has_kv=True,
+                            positions=pos.cuda(), token_seq=torch.zeros(T, dtype=torch.int32).cuda(), offset=off,
+                            eps=1e-5, rotation=rotation, norm_after=after, out_float32=True).cpu().double()
+    x = rows.double()
+    for t in range(T):
+        q = plain.rotate(x[t, off:off + hq * d].view(hq, d), int(pos[t]), r)
+        k = plain.rotate(x[t, off + hq * d:off + (hq + hkv) * d].view(hkv, d), int(pos[t]), r)
+        if after:
+            q, k = plain.rms_norm(q, 1e-5), plain.rms_norm(k, 1e-5)
+        want = torch.cat([q.reshape(-1), k.reshape(-1), x[t, off + (hq + hkv) * d:off + (hq + hkv) * d + hkv * dv]])
+        # a float32 angle p * f carries a rounding of about 1e-7 of its size: 4e-4 radians at position 4,095
+        tol = 2e-5 + 3e-7 * int(pos[t])
+        assert (got[t] - want).abs().max() <= tol * max(1.0, want.abs().max()), t
+
+
+def attention_plain(q, keys, values, scale, softcap):
+    """q [Hq, d]; keys [n, Hkv, d]; values [n, Hkv, dv]: the visible keys only. Returns [Hq * dv]."""
+    per = q.shape[0] // keys.shape[1]
+    out = []
+    for h in range(q.shape[0]):
+        s = (keys[:, h // per] @ q[h]) * scale
+        if softcap:
+            s = softcap * torch.tanh(s / softcap)
+        out.append(plain.softmax_mix(s, values[:, h // per]))
+    return torch.cat(out)
+
+
+ATTENTION_SHAPES = [
+    # hq, hkv, d, dv, page, window, [(context, q_len)]
+    (6, 2, 20, 12, 8, 0, [(37, 37), (50, 1), (9, 2)]),                       # rows of [k | v]: the float32-arithmetic kernel
+    (3, 1, 8, 40, 4, 7, [(130, 1), (17, 17)]),
+    (4, 4, 24, 24, 16, 33, [(100, 100), (90, 1)]),                           # two planes, sizes the tensor cores do not take
+    (8, 2, 64, 64, 16, 0, [(130, 130), (129, 1), (200, 2)]),                 # two planes: the tensor-core kernels
+    (8, 4, 128, 128, 64, 0, [(1500, 1), (1, 1), (256, 1), (257, 1), (700, 513)]),
+    (4, 4, 128, 128, 64, 130, [(1300, 897), (64, 64), (65, 1), (131, 1), (130, 1)]),
+    (6, 2, 64, 64, 16, 40, [(150, 150), (131, 1), (90, 3)]),
+    (5, 1, 128, 128, 32, 0, [(300, 1), (70, 70), (33, 2)]),
+]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("pairs", [False, True])
+@pytest.mark.parametrize("hq,hkv,d,dv,page,window,work", ATTENTION_SHAPES)
+def test_attention_with_capped_scores_and_windows(monkeypatch, dtype, pairs, hq, hkv, d, dv, page, window, work):
+    """Scores through cap * tanh(s / cap), with queries large enough that the cap bites, alone and behind a window, in
+    every attention kernel that a layer of this kind can reach."""
+    from tinyinfer_b200 import ops
+    if pairs and (d != dv or d < 128 or dtype == torch.float32):
+        pytest.skip("one CTA pair form")
+    monkeypatch.setattr(ops, "PAIR_MIN_CTAS", 0 if pairs else 1 << 30)
+    gen = torch.Generator().manual_seed(hq * d)
+    lens = [c for c, _ in work]
+    pages_of = [(n + page - 1) // page for n in lens]
+    total = sum(pages_of) + 3
+    perm = torch.randperm(total, generator=gen).tolist()
+    width = max(pages_of)
+    tables, nxt = [], 0
+    for nb in pages_of:
+        tables.append(perm[nxt:nxt + nb] + [-1] * (width - nb))
+        nxt += nb
+    bt = torch.tensor(tables, dtype=torch.int32)
+    planes = d == dv
+    cache = torch.full((2, total, hkv, page, d) if planes else (1, total, hkv, page, d + dv), float("nan"), dtype=dtype)
+    ks = [torch.randn(n, hkv, d, generator=gen).to(dtype) for n in lens]
+    vs = [torch.randn(n, hkv, dv, generator=gen).to(dtype) for n in lens]
+    for i, n in enumerate(lens):
+        for p in range(n):
+            pg = tables[i][p // page]
+            if planes:
+                cache[0, pg, :, p % page], cache[1, pg, :, p % page] = ks[i][p], vs[i][p]
+            else:
+                cache[0, pg, :, p % page] = torch.cat([ks[i][p], vs[i][p]], dim=-1)
+    pos = torch.tensor([p for c, n in work for p in range(c - n, c)], dtype=torch.int32)
+    seq = torch.tensor([i for i, (c, n) in enumerate(work) for _ in range(n)], dtype=torch.int32)
+    T = pos.shape[0]
+    q = (3.0 * torch.randn(T, hq, d, generator=gen)).to(dtype)
+    cap, scale = 4.0, d ** -0.5
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    args = dict(positions=pos.cuda(), token_seq=seq.cuda(), block_table=bt.cuda(), scale=scale, status=status,
+                window=window or None, softcap=cap)
+    if planes:
+        out = ops.paged_attention(q.cuda(), cache.cuda(), **args)
+    else:
+        out = ops.attention_rows(q.cuda(), cache.cuda(), v_dim=dv, **args)
+    assert int(status.item()) == 0
+    out = out.cpu().double()
+    worst, bites = 0.0, 0
+    for t in range(T):
+        i, p = int(seq[t]), int(pos[t])
+        lo = plain.visible(p, window)
+        want = attention_plain(q[t].double(), ks[i][lo:p + 1].double(), vs[i][lo:p + 1].double(), scale, cap)
+        bites += int(((ks[i][lo:p + 1, 0].double() @ q[t, 0].double()) * scale).abs().max() > cap)
+        worst = max(worst, float((out[t] - want).abs().max()))
+    assert bites > 0
+    assert worst <= (2e-5 if dtype == torch.float32 else 2e-2), worst
+
+
+@pytest.mark.parametrize("heads,rank,rot,page,window,work", [
+    (3, 24, 8, 8, 19, [(37, 37), (50, 1), (9, 2), (20, 1), (19, 1)]),
+    (4, 64, 16, 16, 50, [(130, 130), (129, 1), (200, 2), (51, 1), (50, 1)]),
+    (16, 256, 64, 64, 300, [(700, 513), (1500, 1), (301, 1), (300, 1)]),
+    (5, 20, 4, 4, 0, [(70, 70), (33, 2)]),
+    (2, 8, 8, 16, 1, [(40, 40), (17, 1)]),
+])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_latent_attention_behind_a_window(heads, rank, rot, page, window, work, dtype):
+    """The attention over cached latent rows with a window, in the float32-arithmetic kernel and (bfloat16, through a
+    step's layout) on the tensor cores, prompt portions and decoded tokens, the window's edge inside a portion."""
+    from tinyinfer_b200 import ops
+    from tinyinfer_b200.engine.batch import BatchBuffers, StepEntry
+    gen = torch.Generator().manual_seed(heads * rank)
+    dk = rank + rot
+    lens = [c for c, _ in work]
+    pages_of = [(n + page - 1) // page for n in lens]
+    total = sum(pages_of) + 2
+    perm = torch.randperm(total, generator=gen).tolist()
+    tables, nxt = [], 0
+    for nb in pages_of:
+        tables.append(perm[nxt:nxt + nb])
+        nxt += nb
+    cache = torch.full((1, total, 1, page, dk), float("nan"), dtype=dtype)
+    rows = [torch.randn(n, dk, generator=gen).to(dtype) for n in lens]
+    for i, n in enumerate(lens):
+        for p in range(n):
+            cache[0, tables[i][p // page], 0, p % page] = rows[i][p]
+    buffers = BatchBuffers(torch.device("cuda"), sum(n for _, n in work), len(work), max(pages_of), 1)
+    entries = [StepEntry(i, [0] * n, []) for i, (_, n) in enumerate(work)]
+    step = buffers.build(entries, [c - n for c, n in work], [0] * len(work), [tables])
+    T = step.num_tokens
+    q = (2.0 * torch.randn(T, heads * dk, generator=gen)).float()
+    scale = dk ** -0.5
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    got = {}
+    for name, ctx in (("arithmetic", None), ("tensor cores", step)):
+        if ctx is not None and dtype == torch.float32:
+            continue
+        got[name] = ops.latent_attention(q.cuda(), cache.cuda(), heads=heads, rank=rank, rot=rot, scale=scale, sink=None,
+                                         positions=step.positions, token_seq=step.token_seq, block_table=step.block_tables[0],
+                                         max_context=max(lens), window=window or None, step=ctx, status=status).cpu().double()
+    assert int(status.item()) == 0
+    pos, seq = step.positions.cpu().tolist(), step.token_seq.cpu().tolist()
+    for name, out in got.items():
+        worst = 0.0
+        for t in range(T):
+            i, p = seq[t], pos[t]
+            keys = rows[i][plain.visible(p, window):p + 1].double()
+            qt = q[t].double().view(heads, dk)
+            if name == "tensor cores":
+                qt = qt.to(torch.bfloat16).double()             # that kernel's query rows are bfloat16 operands
+            want = torch.cat([plain.softmax_mix((keys @ qt[h]) * scale, keys[:, :rank]) for h in range(heads)])
+            worst = max(worst, float((out[t] - want).abs().max()))
+        assert worst <= (2e-5 if dtype == torch.float32 else 2e-2), (name, worst)
+
+
+@pytest.mark.parametrize("experts,top,ff,width,tokens", [(5, 2, 24, 72, 37), (1, 1, 16, 40, 9), (3, 3, 8, 40, 5), (16, 4, 64, 128, 600),
+                                                         (4, 2, 128, 128, 1000)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_experts_scored_by_sigmoids_and_weighted_at_their_input(experts, top, ff, width, tokens, dtype):
+    """Sigmoid scores, the largest chosen, the score times the token's row as the expert's input, silu(gate) * up, the
+    plain sum of the outputs: op by op as the experts' part strings them together, in every form of the grouped
+    products that the token counts reach."""
+    from tinyinfer_b200 import ops
+    gen = torch.Generator().manual_seed(experts * 7 + top)
+    x = torch.randn(tokens, width, generator=gen).to(dtype)
+    router = (3.0 * torch.randn(experts, width, generator=gen) / width ** 0.5).to(dtype)
+    up = (torch.randn(experts, 2 * ff, width, generator=gen) / width ** 0.5).to(dtype)
+    down = (torch.randn(experts, width, ff, generator=gen) / ff ** 0.5).to(dtype)
+    xd = x.cuda()
+    routing = ops.route_experts(xd, router.cuda(), top, 0.0, tile_rows=ops.expert_tile_rows(xd, experts, top, ff),
+                                renormalize=False, real_experts=experts, scoring="sigmoid")
+    scores = torch.sigmoid(x.double() @ router.double().t())
+    ranked = torch.sort(scores, dim=-1, descending=True).values
+    clear = (ranked[:, top - 1] - ranked[:, top]) > 1e-3 if top < experts else torch.ones(tokens, dtype=torch.bool)
+    got_chosen = routing.chosen.cpu().long()
+    assert clear.float().mean() > 0.9
+    assert torch.equal(torch.sort(got_chosen[clear], dim=-1).values, torch.sort(torch.topk(scores, top).indices[clear], dim=-1).values)
+    assert (routing.weight.cpu().double() - torch.gather(scores, 1, got_chosen)).abs().max() < 1e-5
+    assert float(routing.weight.sum(-1).max()) > 1.0 or top == 1        # sigmoids do not share one unit between them
+    gate_up = ops.expert_linear(xd, up.cuda(), routing, up=True, activation=False, weighted_input=True)
+    rows = ops.expert_linear(ops.silu_glu(gate_up), down.cuda(), routing, up=False)
+    got = ops.experts_combine(rows, xd, routing, experts, weighted=False).cpu().double()
+    want = torch.zeros(tokens, width, dtype=torch.float64)
+    for t in range(tokens):
+        for c in range(top):
+            e = int(got_chosen[t, c])
+            h = scores[t, e] * x[t].double()
+            if dtype == torch.bfloat16:
+                h = h.to(dtype).double()
+            gu = up[e].double() @ h
+            if dtype == torch.bfloat16:
+                gu = gu.to(dtype).double()
+            y = plain.silu(gu[:ff]) * gu[ff:]
+            if dtype == torch.bfloat16:
+                y = y.to(dtype).double()
+            want[t] += down[e].double() @ y
+    assert (got - want).abs().max() <= (2e-5 if dtype == torch.float32 else 3e-2) * max(1.0, want.abs().max())
+
+
+def test_update_norm_in_the_stream_step_and_gate_behind_a_batched_product():
+    from tinyinfer_b200 import ops
+    gen = torch.Generator().manual_seed(5)
+    for width in (40, 72, 256):
+        for dtype in (torch.float32, torch.bfloat16):
+            x = torch.randn(1, 9, width, generator=gen)
+            y = (3.0 * torch.randn(9, width, generator=gen)).to(dtype)
+            wb, wn = 1 + 0.3 * torch.randn(width, generator=gen), 1 + 0.3 * torch.randn(width, generator=gen)
+            one = torch.ones(1, device="cuda")
+            xd = x.clone().cuda()
+            pending = ops.StreamUpdate(y.cuda(), torch.ones(1, 1, device="cuda"), one, norm_weight=wb.cuda(), norm_eps=1e-5)
+            h = ops.streams_step(xd, pending, one, wn.cuda(), 1e-6, torch.float32).cpu().double()
+            want_x = x[0].double() + plain.rms_norm(y.double(), 1e-5, wb.double())
+            assert (xd.cpu()[0].double() - want_x).abs().max() < 1e-5
+            assert (h - plain.rms_norm(want_x, 1e-6, wn.double())).abs().max() < 1e-5
+    for dtype, tol in ((torch.float32, 1e-5), (torch.bfloat16, 2e-2)):
+        for heads, n, k in ((3, 20, 24), (4, 32, 64)):
+            x = torch.randn(13, heads * k, generator=gen).to(dtype)
+            w = (torch.randn(heads, n, k, generator=gen) / k ** 0.5).to(dtype)
+            gate = torch.randn(13, 5 + heads * n, generator=gen).to(dtype)
+            got = ops.batched_linear(x.cuda(), w.cuda(), x_batch_stride=k, k=k, gate=gate.cuda(), gate_offset=5).cpu().double()
+            want = torch.einsum("thk,hnk->thn", x.double().view(13, heads, k), w.double()).reshape(13, heads * n)
+            want = want * torch.sigmoid(gate[:, 5:].double())
+            assert (got - want).abs().max() <= tol * max(1.0, want.abs().max())
+
+
+# ------------------------------------------------------------------ each mechanism alone
+def single(kind, mlp=None, **kw):
+    if kind == "attention":
+        layers = [fh.layer("attention", fh.attention(6, 2, 20, 12, scale=0.35, rot_=fh.rot(1e4, 12, fh.scaling(3.0, 20)), softcap=3.0), mlp)]
+    elif kind == "attention_planes":
+        layers = [fh.layer("attention", fh.attention(4, 2, 64, 64, scale=0.2, rot_=fh.rot(1e4, 32, fh.scaling(4.0, 32)), softcap=6.0), mlp)]
+    elif kind == "windowed":
+        layers = [fh.layer("attention_2", fh.attention(6, 3, 12, 20, scale=0.4, rot_=fh.rot(1e4, 8), window=13), mlp)]
+    elif kind == "windowed_planes":
+        layers = [fh.layer("attention_2", fh.attention(4, 2, 128, 128, scale=0.08, rot_=fh.rot(1e6, 128), window=37), mlp)]
+    elif kind == "latent":
+        layers = [fh.layer("latent_attention", fh.latent(3, 12, 8, 20, 24, scaled=fh.scaling(2.0, 16, 4.0), window=21), mlp)]
+    elif kind == "shared":
+        first = fh.layer("latent_attention", fh.latent(2, 8, 8, 8, 16, window=9), mlp)
+        layers = [first, fh.shared([first], 0), fh.shared([first], 0)]
+    else:
+        raise ValueError(kind)
+    return fh.config(layers, **kw)
+
+
+@pytest.mark.parametrize("kind,mlp", [("attention", None), ("attention_planes", None), ("windowed", None), ("windowed_planes", None),
+                                      ("latent", None), ("shared", None), ("windowed", fh.moe(6, 2, 24)), ("latent", fh.moe(4, 4, 16)),
+                                      ("attention", fh.moe(3, 1, 40))])
+def test_one_mechanism_alone(tmp_path, kind, mlp):
+    cfg = single(kind, mlp)
+    folder = fh.write_folder(tmp_path / "m", cfg, seed=11)
+    requests = fh.random_requests(cfg, [75, 1, 2, 19], seed=4)
+    want = fh.plain_logits(folder, requests)
+    for steps in (helpers.trace_whole(requests), helpers.trace_chunked(requests, seed=3), helpers.trace_decode_tail(requests, tail=80)):
+        got, _ = run(folder, "float32", steps, page=8)
+        assert helpers.first_bad(got, want, TOL["float32"]) is None
+    folder16 = fh.write_folder(tmp_path / "m16", cfg, seed=11, dtype="bfloat16")
+    want16 = fh.plain_logits(folder16, requests)
+    for steps in (helpers.trace_whole(requests), helpers.trace_decode_tail(requests, tail=40)):
+        got, _ = run(folder16, "bfloat16", steps, page=16)
+        assert agrees(got, want16, "bfloat16"), np.sort(row_errors(got, want16))[-5:]
+
+
+def test_residual_after_every_layer(tmp_path):
+    """The float32 stream after every layer run of a prompt (a layer whose tensors run twice counts twice)."""
+    from tinyinfer_b200 import ops
+    from tinyinfer_b200.engine.replay import TraceSession
+    cfg = fh.MIX
+    folder = fh.write_folder(tmp_path / "m", cfg, seed=2)
+    tokens = fh.random_requests(cfg, [23], seed=1)["r0"]
+    c, w = fh.read_folder(folder)
+    per_token = []
+    fh.forward(c, w, tokens, residuals=per_token)
+    want = torch.stack(per_token).permute(1, 0, 2)                 # [layer runs, tokens, width]
+    session = TraceSession(folder, "float32", 64, page_size=8, cuda_graphs=False)
+    got = []
+    for block in session.model.blocks:      # a block returns the stream and the update that the next norm applies
+        inner = block.forward_linked
+
+        def watched(x, link, next_norm, step, cache, _inner=inner):
+            (stream, pending), _ = _inner(x, link, next_norm, step, cache)
+            ops.streams_step(stream, pending, None, None, 0.0, torch.float32)       # applies the update, reads nothing
+            got.append(stream[0].detach().cpu().double().clone())
+            return (stream, None), None
+        block.forward_linked = watched
+    session.run_step({"step": 0, "entries": [{"id": "a", "tokens": tokens, "want": [len(tokens) - 1]}], "end": ["a"]})
+    assert len(got) == len(cfg["layers"]) == 6
+    for i, rows in enumerate(got):
+        assert (rows - want[i]).abs().max() <= 2e-5 * want[i].abs().max(), i
+
+
+# ------------------------------------------------------------------ whole models, every cut
+def traces_for(requests, max_live=4):
+    return {"whole": helpers.trace_whole(requests), "tail": helpers.trace_decode_tail(requests, tail=32),
+            "chunked": helpers.trace_chunked(requests, seed=1), "mixed": helpers.trace_mixed(requests, seed=2, max_live=max_live)}
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name,page", [("MIX", 8), ("WIDE", 16), ("ONE", 4), ("MIX", 64)])
+def test_every_cut_matches_plain(tmp_path, name, page, dtype):
+    cfg = getattr(fh, name)
+    folder = fh.write_folder(tmp_path / name, cfg, seed=3, dtype=dtype)
+    requests = fh.random_requests(cfg, LENGTHS, seed=5)
+    want = fh.plain_logits(folder, requests)
+    results = {}
+    for tag, steps in traces_for(requests).items():
+        got, session = run(folder, dtype, steps, page, max_live=4)
+        assert {r: len(v) for r, v in got.items()} == {r: len(t) for r, t in requests.items()}, tag
+        assert agrees(got, want, dtype), (tag, helpers.first_bad(got, want, TOL[dtype]), np.sort(row_errors(got, want))[-8:])
+        if tag == "mixed" and page < 64:
+            stats = session.runner.manager.stats()
+            assert all(g["pages_taken"] > g["pages"] for g in stats["groups"]), "pages were not used again"
+        results[tag] = got
+    for tag in ("tail", "chunked", "mixed"):        # the cuts against each other: rounding only
+        assert agrees(results[tag], {r: np.stack([results["whole"][r][p] for p in range(len(t))]) for r, t in requests.items()},
+                      dtype), tag
+
+
+def test_pages_change_hands_between_many_requests(tmp_path):
+    """Two requests live at a time: pages of finished requests, and pages that a window has passed, go to new owners."""
+    cfg = fh.MIX
+    folder = fh.write_folder(tmp_path / "m", cfg, seed=8)
+    requests = fh.random_requests(cfg, [30, 9, 41, 2, 17, 55, 5, 26], seed=9)
+    want = fh.plain_logits(folder, requests)
+    steps = helpers.trace_mixed(requests, seed=4, max_live=2, decode_tail=6)
+    got, session = run(folder, "float32", steps, page=4, max_live=2)
+    assert helpers.first_bad(got, want, TOL["float32"]) is None
+    stats = session.runner.manager.stats()
+    assert all(g["pages_taken"] > g["pages"] for g in stats["groups"])
+
+
+def test_batch_of_unequal_requests_equals_each_alone(tmp_path):
+    cfg = fh.WIDE
+    folder = fh.write_folder(tmp_path / "m", cfg, seed=5)
+    requests = fh.random_requests(cfg, [50, 3, 128, 17], seed=2)
+    together = [{"step": 0, "entries": [{"id": r, "tokens": t, "want": list(range(len(t)))} for r, t in requests.items()],
+                 "end": list(requests)}]
+    got, _ = run(folder, "float32", together, page=16)
+    alone, _ = run(folder, "float32", helpers.trace_whole(requests), page=16)
+    want = fh.plain_logits(folder, requests)
+    assert helpers.first_bad(got, want, TOL["float32"]) is None
+    scale = max(float(np.abs(w).max()) for w in want.values())
+    assert max(float(np.abs(got[r][p] - alone[r][p]).max()) for r in requests for p in got[r]) / scale <= 1e-5
+
+
+def test_a_request_left_out_of_steps_goes_on(tmp_path):
+    """A request pauses for some steps while others run and end (their pages change hands meanwhile)."""
+    cfg = fh.MIX
+    folder = fh.write_folder(tmp_path / "m", cfg, seed=4)
+    requests = fh.random_requests(cfg, [40, 21, 33], seed=7)
+    a, b, c = (requests[f"r{i}"] for i in range(3))
+    want = fh.plain_logits(folder, requests)
+    every = lambda toks, lo, hi: {"tokens": toks[lo:hi], "want": list(range(hi - lo))}
+    steps = [
+        {"step": 0, "entries": [dict(id="r0", **every(a, 0, 13)), dict(id="r1", **every(b, 0, 21))], "end": ["r1"]},
+        {"step": 1, "entries": [dict(id="r2", **every(c, 0, 2))], "end": []},
+        {"step": 2, "entries": [dict(id="r2", **every(c, 2, 33))], "end": ["r2"]},
+        {"step": 3, "entries": [dict(id="r0", **every(a, 13, 14))], "end": []},
+        {"step": 4, "entries": [dict(id="r0", **every(a, 14, 40))], "end": ["r0"]},
+    ]
+    got, _ = run(folder, "float32", steps, page=8, max_live=2)
+    assert helpers.first_bad(got, want, TOL["float32"]) is None
+
+
+# ------------------------------------------------------------------ window edges, far keys, page borders, first tokens
+@pytest.mark.parametrize("kind", ["attention_2", "latent_attention"])
+@pytest.mark.parametrize("window,page", [(6, 4), (16, 16), (17, 16), (64, 16), (65, 64), (100, 8)])
+def test_the_key_at_the_edge_of_a_window(tmp_path, kind, window, page):
+    """One windowed layer with sharp scores and no feed-forward. For a late position p, the token at p - window + 1
+    (the oldest key the window keeps) moves the logits at p and the token at p - window does not, in the plain
+    statement; the engine agrees with it on all three prompts, in a prompt's portion and decoded token by token."""
+    mixer = (fh.attention(2, 1, 16, 24, scale=0.6, rot_=fh.rot(100.0, 8), window=window) if kind == "attention_2"
+             else fh.latent(2, 12, 4, 24, 16, scale=0.9, window=window))
+    cfg = fh.config([fh.layer(kind, mixer, None)], width=32)
+    folder = fh.write_folder(tmp_path / "m", cfg, seed=window)
+    n = window + 40
+    base = fh.random_requests(cfg, [n], seed=3)["r0"]
+    p = n - 3
+    inside, outside = list(base), list(base)
+    inside[p - window + 1] = (inside[p - window + 1] + 1) % cfg["vocab"]
+    outside[p - window] = (outside[p - window] + 1) % cfg["vocab"]
+    requests = {"r0": base, "r1": inside, "r2": outside}
+    want = fh.plain_logits(folder, requests)
+    scale = np.abs(want["r0"]).max()
+    assert np.abs(want["r2"][p] - want["r0"][p]).max() == 0.0
+    assert np.abs(want["r1"][p] - want["r0"][p]).max() > 20 * TOL["float32"] * scale
+    for steps in (helpers.trace_whole(requests), helpers.trace_decode_tail(requests, tail=window + 10),
+                  helpers.trace_chunked(requests, seed=window)):
+        got, _ = run(folder, "float32", steps, page=page)
+        assert helpers.first_bad(got, want, TOL["float32"]) is None
+
+
+def test_one_far_key_among_hundreds(tmp_path):
+    """One query head is scaled so that the key of one early token outscores all others by a wide margin (the cap is
+    set high enough not to level that out): the logits at the end then hang on that token's value. The same prompt
+    with that token replaced differs at the end; the engine agrees with the plain statement on both, decoded through
+    the cache, at several page sizes, in both number formats."""
+    cfg = fh.config([fh.layer("attention", fh.attention(2, 1, 16, 16, scale=1.0, softcap=40.0), None),
+                     fh.layer("attention", fh.attention(2, 1, 16, 24, scale=1.0, softcap=40.0, rot_=fh.rot(1e4, 8)), fh.moe(2, 1, 32))],
+                    width=32)
+
+    def loud(t):
+        t["l0.mix.q"] *= 6.0
+        t["l0.mix.q.b"] *= 0.0
+    folder = fh.write_folder(tmp_path / "m", cfg, seed=5, edit=loud)
+    base = fh.random_requests(cfg, [300], seed=3)["r0"]
+    c, w = fh.read_folder(folder)
+    full = fh.forward(c, w, base)
+    moves = {}
+    for p in (3, 15, 16, 17, 31, 32, 63, 64, 65):
+        other = list(base)
+        other[p] = (other[p] + 1) % cfg["vocab"]
+        moves[p] = float(np.abs(fh.forward(c, w, other)[-1] - full[-1]).max())
+    far = max(moves, key=moves.get)
+    assert moves[far] > 1e-3 * np.abs(full).max()
+    changed = list(base)
+    changed[far] = (changed[far] + 1) % cfg["vocab"]
+    requests = {"r0": base, "r1": changed}
+    want = fh.plain_logits(folder, requests)
+    for page in (4, 16, 64):
+        got, _ = run(folder, "float32", helpers.trace_decode_tail(requests, tail=40), page=page)
+        assert helpers.first_bad(got, want, TOL["float32"]) is None, page
+
+
+def test_keys_far_back_through_tensor_core_attention(tmp_path):
+    """A context of 700 tokens through heads of 64 and 128 features (the tensor-core kernels in bfloat16), whole, with a
+    long decoded tail across page and key-tile borders, and in portions."""
+    cfg = fh.WIDE
+    requests = fh.random_requests(cfg, [700], seed=13)
+    folder = fh.write_folder(tmp_path / "m", cfg, seed=21)
+    want = fh.plain_logits(folder, requests)
+    for steps in (helpers.trace_whole(requests), helpers.trace_decode_tail(requests, tail=140), helpers.trace_chunked(requests, seed=7)):
+        got, _ = run(folder, "float32", steps, page=16)
+        assert helpers.first_bad(got, want, TOL["float32"]) is None
+    folder16 = fh.write_folder(tmp_path / "m16", cfg, seed=21, dtype="bfloat16")
+    want16 = fh.plain_logits(folder16, requests)
+    for steps in (helpers.trace_whole(requests), helpers.trace_decode_tail(requests, tail=140), helpers.trace_chunked(requests, seed=7)):
+        got, _ = run(folder16, "bfloat16", steps, page=16)
+        assert agrees(got, want16, "bfloat16"), np.sort(row_errors(got, want16))[-5:]
+
+
+def test_the_first_tokens(tmp_path):
+    """Position zero (no rotation angle, a softmax of one key, windows not yet full), then the next few, as prompts of
+    one to six tokens and decoded one by one from the start."""
+    for cfg in (fh.MIX, fh.ONE):
+        folder = fh.write_folder(tmp_path / str(cfg["width"]), cfg, seed=12)
+        requests = fh.random_requests(cfg, [1, 2, 3, 4, 5, 6], seed=8)
+        want = fh.plain_logits(folder, requests)
+        got, _ = run(folder, "float32", helpers.trace_whole(requests), page=4)
+        assert helpers.first_bad(got, want, TOL["float32"]) is None
+        got, _ = run(folder, "float32", helpers.trace_decode_tail(requests, tail=6), page=4)
+        assert helpers.first_bad(got, want, TOL["float32"]) is None
+
+
+# ------------------------------------------------------------------ long decoding through graphs
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["MIX", "WIDE"])
+def test_long_decoding_replays_graphs(tmp_path, name, dtype):
+    cfg = getattr(fh, name)
+    folder = fh.write_folder(tmp_path / "m", cfg, seed=6, dtype=dtype)
+    requests = fh.random_requests(cfg, [160, 150], seed=1)
+    want = fh.plain_logits(folder, requests)
+    steps = [{"step": 0, "entries": [{"id": r, "tokens": t[:4], "want": [0, 1, 2, 3]} for r, t in requests.items()], "end": []}]
+    for p in range(4, 150):
+        steps.append({"step": p, "entries": [{"id": r, "tokens": [t[p]], "want": [0]} for r, t in requests.items()],
+                      "end": list(requests) if p == 149 else []})
+    got, session = run(folder, dtype, steps, page=8 if name == "MIX" else 16)
+    assert session.runner.graph_replays > 100
+    assert agrees(got, {r: w[:150] for r, w in want.items()}, dtype)
+
+
+# ------------------------------------------------------------------ generation through the entry point
+@pytest.mark.parametrize("dtype,tol", [("float32", 1e-4), ("bfloat16", 6e-2)])
+def test_greedy_generation_through_the_scheduler(tmp_path, dtype, tol):
+    from tinyinfer_b200 import LLM
+    from tinyinfer_b200.sampling import SamplingParams
+    cfg = fh.MIX
+    folder = fh.write_folder(tmp_path / "m", cfg, seed=3, dtype=dtype)
+    llm = LLM(folder, dtype=dtype, max_num_batched_tokens=24, max_num_seqs=3, kvcache_block_size=8,
+              num_kvcache_blocks=40, prefill_chunk=9, max_model_len=128)
+    prompts = list(fh.random_requests(cfg, [1, 7, 16, 33, 50], seed=6).values())
+    outs = llm.generate(prompts, SamplingParams(greedy=True, max_tokens=10))
+    c, w = fh.read_folder(folder)
+    missed = 0
+    for p, o in zip(prompts, outs):
+        assert o["all_token_ids"] == p + o["token_ids"] and len(o["token_ids"]) == 10
+        logits = fh.forward(c, w, p + o["token_ids"])
+        for i, tok in enumerate(o["token_ids"]):          # teacher forcing: the token has (nearly) the largest plain logit
+            row = logits[len(p) - 1 + i]
+            missed += int(not row.max() - row[tok] <= tol * np.abs(logits).max())
+    # bfloat16: a router's close call that falls the other way gives a token another expert, and another next token
+    assert missed <= (0 if dtype == "float32" else 3)
+    assert not llm.runner.manager.live_requests
+    llm.runner.manager.check_consistency()
+    llm.close()
+
+
+def test_command_line_generates_with_a_folder_and_with_a_preset(tmp_path):
+    import json
+    import subprocess
+    import sys
+    from pathlib import Path
+    root = Path(__file__).resolve().parent.parent
+    folder = fh.write_folder(tmp_path / "m", fh.ONE, seed=3)
+    common = ["--dtype", "fp32", "--prompt-ids", "5,17,3,200", "--prompt-len", "9", "--greedy", "--max-tokens", "6",
+              "--max-num-seqs", "2", "--max-num-batched-tokens", "16", "--block-size", "4", "--num-kvcache-blocks", "32",
+              "--max-model-len", "64"]
+    res = subprocess.run([sys.executable, str(root / "examples" / "generate.py"), "--model", str(folder)] + common,
+                         capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stderr[-2000:]
+    rows = [json.loads(l) for l in res.stdout.splitlines() if l.startswith("{")]
+    assert len(rows) == 2 and all(len(r["token_ids"]) == 6 for r in rows)
+    c, w = fh.read_folder(folder)
+    logits = fh.forward(c, w, [5, 17, 3, 200] + rows[0]["token_ids"])
+    for i, tok in enumerate(rows[0]["token_ids"]):
+        assert logits[3 + i].max() - logits[3 + i][tok] <= 1e-4 * np.abs(logits).max()
+    res = subprocess.run([sys.executable, str(root / "examples" / "generate.py"), "--random-config", "fezozen-tiny"] + common,
+                         capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stderr[-2000:]
+
+
+def test_trace_runner_program(tmp_path):
+    """The replay program itself: steps on standard input, a file of logits per step that wants some, 'done' lines."""
+    import json
+    import subprocess
+    from pathlib import Path
+    root = Path(__file__).resolve().parent.parent
+    cfg = fh.ONE
+    folder = fh.write_folder(tmp_path / "m", cfg, seed=9, dtype="bfloat16")
+    requests = fh.random_requests(cfg, [20, 70, 9], seed=2)
+    steps = helpers.trace_mixed(requests, seed=1, max_live=3, decode_tail=5)
+    out = tmp_path / "out"
+    out.mkdir()
+    res = subprocess.run([str(root / "bin" / "trace_run"), "--model", str(folder), "--dtype", "float32", "--out", str(out),
+                          "--max-tokens", str(helpers.peak_tokens(steps))], input="".join(json.dumps(s) + "\n" for s in steps),
+                         capture_output=True, text=True, timeout=1200)
+    assert res.returncode == 0, res.stderr[-2000:]
+    assert [l for l in res.stdout.splitlines() if l.startswith("done ")] == [f"done {s['step']}" for s in steps]
+    want = fh.plain_logits(folder, requests)
+    upto = {}
+    for s in steps:
+        wanted = [(e["id"], upto.get(e["id"], 0) + p) for e in s["entries"] for p in e["want"]]
+        for e in s["entries"]:
+            upto[e["id"]] = upto.get(e["id"], 0) + len(e["tokens"])
+        rows = np.fromfile(out / f"{s['step']}.f32", dtype="<f4").reshape(len(wanted), cfg["vocab"])
+        for row, (rid, p) in zip(rows, wanted):
+            assert np.abs(row - want[rid][p]).max() <= TOL["float32"] * np.abs(want[rid]).max()
+
+
+def random_config(seed):
+    """A model of random sizes and layer order: odd head counts and sizes, windows from one key to beyond the prompt,
+    partial, whole and no rotation with and without a blend, layers that run another's tensors (listed before or after
+    it), with and without experts, one to four of them chosen."""
+    rng = random.Random(seed)
+    width = rng.choice([40, 72, 100, 136])
+    layers = []
+    for i in range(rng.randint(2, 6)):
+        own = [j for j, l in enumerate(layers) if l.get("weights_of") is None]
+        if own and rng.random() < 0.3:
+            layers.append(fh.shared(layers, rng.choice(own)))
+            continue
+        mlp = None
+        if rng.random() > 0.2:
+            experts = rng.randint(1, 9)
+            mlp = fh.moe(experts, rng.randint(1, min(4, experts)), rng.choice([8, 24, 40]))
+        kind = rng.choice(["attention", "attention_2", "latent_attention"])
+        window = rng.choice([None, 1, 2, 7, 16, 33, 64, 200])
+        blend = rng.choice([None, fh.scaling(rng.choice([2.0, 4.0, 8.0]), rng.choice([16, 64, 512]), rng.choice([4.0, 32.0]), rng.choice([0.5, 1.0]))])
+        base = rng.choice([100.0, 10000.0, 5e5])
+        if kind == "latent_attention":
+            layers.append(fh.layer(kind, fh.latent(rng.randint(1, 5), rng.choice([8, 12, 20]), rng.choice([2, 4, 8, 12]), rng.choice([4, 12, 20, 40]),
+                                                   rng.choice([8, 12, 24, 40]), base=base, scaled=blend, window=window), mlp))
+            continue
+        kv = rng.randint(1, 3)
+        d = rng.choice([8, 12, 20, 40, 64])
+        dims = rng.choice([0, 4, d // 2 // 2 * 2, d])
+        m = fh.attention(kv * rng.randint(1, 3), kv, d, d if rng.random() < 0.4 else rng.choice([4, 8, 24, 36]),
+                         scale=rng.uniform(0.1, 0.5), rot_=fh.rot(base, dims, blend) if dims else None,
+                         softcap=rng.choice([None, 2.0, 30.0]) if kind == "attention" else None,
+                         window=window if kind == "attention_2" or rng.random() < 0.3 else None)
+        layers.append(fh.layer(kind, m, mlp))
+    if rng.random() < 0.5:            # a layer listed before the one whose tensors it runs
+        j = rng.choice([j for j, l in enumerate(layers) if l.get("weights_of") is None])
+        layers.insert(0, fh.shared(layers, j))
+        for l in layers[1:]:
+            if l.get("weights_of") is not None:
+                l["weights_of"] += 1
+        layers[0]["weights_of"] = j + 1
+    return fh.config(layers, vocab=rng.choice([97, 256, 300]), width=width, eps=rng.choice([1e-5, 1e-6]), scale=rng.choice([1.0, 3.0, 7.5]))
+
+
+@pytest.mark.parametrize("seed", [1, 2, 3, 4, 5, 6, 7, 8])
+def test_models_of_random_sizes_and_orders(tmp_path, seed):
+    cfg = random_config(seed)
+    page = [4, 8, 16, 32, 64, 16, 8, 4][seed - 1]
+    requests = fh.random_requests(cfg, [70, 1, 37, 150, 2, 64], seed=seed)
+    folder = fh.write_folder(tmp_path / "m", cfg, seed=seed)
+    want = fh.plain_logits(folder, requests)
+    for steps in (helpers.trace_whole(requests), helpers.trace_mixed(requests, seed=seed, max_live=3, decode_tail=20)):
+        got, _ = run(folder, "float32", steps, page, max_live=3)
+        assert helpers.first_bad(got, want, TOL["float32"]) is None, cfg
+    folder16 = fh.write_folder(tmp_path / "m16", cfg, seed=seed, dtype="bfloat16")
+    got, _ = run(folder16, "bfloat16", helpers.trace_mixed(requests, seed=seed, max_live=3, decode_tail=20), page, max_live=3)
+    err = row_errors(got, fh.plain_logits(folder16, requests))
+    assert np.isfinite(err).all() and np.median(err) <= TOL["bfloat16"] / 2, (np.median(err), cfg)

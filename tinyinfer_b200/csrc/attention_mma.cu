@@ -42,6 +42,7 @@ struct AttnParams {
     int max_blocks, hq, hkv, page_size, num_pages, window, num_rows;
     int num_ctas;                  // CTAs of the split kernel: the runs are cut for this many
     float scale_log2;              // softmax scale times log2(e)
+    float cap_log2, cap_arg;       // scores capped by a tanh (ti_score_log2); 0: not
     int has_sink;                  // the softmax denominator holds one more term 2^sink_log2 that has no value
     float sink_log2, out_scale;    // out_scale multiplies the output before its rounding
     const float* head_sinks;         // float32 [query heads]: a sink's logit per head in place of sink_log2 (or null)
@@ -346,7 +347,7 @@ __global__ void __launch_bounds__(THREADS) decode_attention_kernel(const __grid_
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         const int tok = tok0 + nb * 8 + c + (j & 1);
-                        const float v = (tok >= k_begin && tok < k_end) ? sc[nb][j] * p.scale_log2 : -INFINITY;
+                        const float v = (tok >= k_begin && tok < k_end) ? ti_score_log2(p, sc[nb][j]) : -INFINITY;
                         sc[nb][j] = v;
                         mx[j >> 1] = fmaxf(mx[j >> 1], v);
                     }
@@ -673,7 +674,7 @@ TI_API int ti_attention_decode_sink_bf16(void* out, const void* q, const void* k
                                          const int* block_table, int max_blocks, int hq, int hkv, int d, int page_size,
                                          int num_pages, float scale, int window, int max_context, int has_sink, float sink,
                                          float out_scale, const float* head_sinks, const void* gate, int ld_gate, int gate_off,
-                                         int* status, cudaStream_t stream) {
+                                         float softcap, int* status, cudaStream_t stream) {
     if (check_shape(hq, hkv, d, page_size, "attention_decode")) return -1;
     TI_REQUIRE(num_rows >= 0 && num_rows <= 65535 && max_context > 0, "attention_decode: bad sizes");
     if (num_rows == 0) return 0;
@@ -691,6 +692,7 @@ TI_API int ti_attention_decode_sink_bf16(void* out, const void* q, const void* k
     p.rows = rows; p.positions = positions; p.token_seq = token_seq; p.block_table = block_table;
     p.max_blocks = max_blocks; p.hq = hq; p.hkv = hkv; p.page_size = page_size; p.num_pages = num_pages;
     p.window = window; p.scale_log2 = scale * 1.4426950408889634f; p.status = status;
+    TI_SET_SCORE_CAP(p, scale, softcap);
     p.has_sink = has_sink || head_sinks ? 1 : 0; p.sink_log2 = sink * 1.4426950408889634f; p.out_scale = out_scale;
     p.head_sinks = head_sinks; p.gate = (const __nv_bfloat16*)gate; p.ld_gate = ld_gate; p.gate_off = gate_off;
     p.num_rows = num_rows; p.num_ctas = ctas;
@@ -738,7 +740,7 @@ TI_API int ti_attention_decode_bf16(void* out, const void* q, const void* kv_cac
                                     cudaStream_t stream) {
     return ti_attention_decode_sink_bf16(out, q, kv_cache, scratch, scratch_floats, rows, num_rows, positions, token_seq,
                                          block_table, max_blocks, hq, hkv, d, page_size, num_pages, scale, window, max_context,
-                                         0, 0.f, 1.f, nullptr, nullptr, 0, 0, status, stream);
+                                         0, 0.f, 1.f, nullptr, nullptr, 0, 0, 0.f, status, stream);
 }
 
 // ------------------------------------------------------------------------------------------------

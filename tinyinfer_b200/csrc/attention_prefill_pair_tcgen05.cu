@@ -59,6 +59,7 @@ struct PairParams {
     const int* block_table;
     int max_blocks, hq, hkv, page_size, num_pages, window;
     float scale_log2;
+    float cap_log2, cap_arg;         // scores capped by a tanh (ti_score_log2); 0: not
     int has_sink;                    // the softmax denominator holds one more term 2^sink_log2 that has no value
     float sink_log2, out_scale;      // out_scale multiplies the output before its rounding
     const float* head_sinks;         // float32 [query heads]: a sink's logit per head in place of sink_log2 (or null)
@@ -337,7 +338,7 @@ prefill_attention_pair_kernel(const __grid_constant__ CUtensorMap q_map, const _
                     m4[k & 3] = fmaxf(m4[k & 3], __uint_as_float(sr[k]));
                 }
             }
-            const float mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])) * p.scale_log2;   // the scale is positive
+            const float mx = ti_score_log2(p, fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])));   // the scale is positive, a cap rises with the score
             // The reference maximum moves only when the row's maximum has outgrown it by RESCALE_STEP.
             const bool move = mx > m_ref + RESCALE_STEP || (m_ref == -INFINITY && mx > -INFINITY);
             const float m_new = move ? mx : m_ref;
@@ -353,7 +354,7 @@ prefill_attention_pair_kernel(const __grid_constant__ CUtensorMap q_map, const _
             for (int k0 = 0; k0 < KT; k0 += 16) {
 #pragma unroll
                 for (int u = 0; u < 16; ++u)
-                    sr[k0 + u] = __float_as_uint(ex2(fmaf(__uint_as_float(sr[k0 + u]), p.scale_log2, -m_use)));
+                    sr[k0 + u] = __float_as_uint(ex2(ti_prob_log2(p, __uint_as_float(sr[k0 + u]), m_use)));
 #pragma unroll
                 for (int u = 0; u < 16; u += 2) {
                     const float a = __uint_as_float(sr[k0 + u]), b = __uint_as_float(sr[k0 + u + 1]);
@@ -448,7 +449,7 @@ TI_API int ti_attention_prefill_pair_sink_bf16(void* out, const void* q, const v
                                                int num_tokens, const int* block_table, int max_blocks, int hq, int hkv, int d,
                                                int page_size, int num_pages, float scale, int window, int has_sink,
                                                float sink, float out_scale, const float* head_sinks, const void* gate,
-                                               int ld_gate, int gate_off, int* status, cudaStream_t stream) {
+                                               int ld_gate, int gate_off, float softcap, int* status, cudaStream_t stream) {
     TI_REQUIRE(d == 64 || d == 128, "attention_prefill_pair: head_dim %d is not 64 or 128", d);
     TI_REQUIRE(hq > 0 && hkv > 0 && hq % hkv == 0, "attention_prefill_pair: bad head counts");
     TI_REQUIRE(num_tiles <= 65535, "attention_prefill_pair: more than 65535 tiles in one step");
@@ -462,6 +463,7 @@ TI_API int ti_attention_prefill_pair_sink_bf16(void* out, const void* q, const v
     p.out = (__nv_bfloat16*)out; p.tiles = tiles; p.block_table = block_table; p.max_blocks = max_blocks;
     p.hq = hq; p.hkv = hkv; p.page_size = page_size; p.num_pages = num_pages; p.window = window;
     p.scale_log2 = scale * 1.4426950408889634f; p.status = status;
+    TI_SET_SCORE_CAP(p, scale, softcap);
     p.has_sink = has_sink || head_sinks ? 1 : 0; p.sink_log2 = sink * 1.4426950408889634f; p.out_scale = out_scale;
     p.head_sinks = head_sinks; p.gate = (const __nv_bfloat16*)gate; p.ld_gate = ld_gate; p.gate_off = gate_off;
     dim3 grid(hq, num_tiles);
@@ -491,5 +493,5 @@ TI_API int ti_attention_prefill_pair_bf16(void* out, const void* q, const void* 
                                           int page_size, int num_pages, float scale, int window, int* status,
                                           cudaStream_t stream) {
     return ti_attention_prefill_pair_sink_bf16(out, q, kv_cache, tiles, num_tiles, num_tokens, block_table, max_blocks, hq, hkv,
-                                               d, page_size, num_pages, scale, window, 0, 0.f, 1.f, nullptr, nullptr, 0, 0, status, stream);
+                                               d, page_size, num_pages, scale, window, 0, 0.f, 1.f, nullptr, nullptr, 0, 0, 0.f, status, stream);
 }

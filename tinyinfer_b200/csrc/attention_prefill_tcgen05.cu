@@ -36,6 +36,7 @@ struct PrefillParams {
     float* part_o;                   // [128-row tile][split][head][row][D] unnormalised outputs
     float* part_ml;                  // [128-row tile][split][head][row][2] maximum (log2 domain) and sum
     float scale_log2;
+    float cap_log2, cap_arg;         // scores capped by a tanh (ti_score_log2); 0: not
     int has_sink;                    // the softmax denominator holds one more term 2^sink_log2 that has no value
     float sink_log2, out_scale;      // out_scale multiplies the output before its rounding
     const float* head_sinks;         // float32 [query heads]: a sink's logit per head in place of sink_log2 (or null)
@@ -270,7 +271,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
             max_xch[b][half][r] = mx;
             asm volatile("bar.sync %0, 64;" ::"r"(1 + lane_group) : "memory");     // the two warps of this row quarter
             mx = fmaxf(mx, max_xch[b][half ^ 1][r]);
-            const float m_new = fmaxf(m_run, mx * p.scale_log2);
+            const float m_new = fmaxf(m_run, ti_score_log2(p, mx));     // the cap rises with the score, like the scale
             const float m_use = m_new == -INFINITY ? 0.f : m_new;
             const float corr = ex2(m_run - m_use);
             m_run = m_new;
@@ -311,13 +312,13 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
                     if (c + 31 <= wmax0 && c > wmin1) {
 #pragma unroll
                         for (int i = 0; i < 32; ++i) {
-                            v[i] = ex2(fmaf(v[i], p.scale_log2, -m_use));
+                            v[i] = ex2(ti_prob_log2(p, v[i], m_use));
                             l_run += v[i];
                         }
                     } else {
 #pragma unroll
                         for (int i = 0; i < 32; ++i) {
-                            v[i] = (c + i <= kmax && c + i > kmin) ? ex2(fmaf(v[i], p.scale_log2, -m_use)) : 0.f;
+                            v[i] = (c + i <= kmax && c + i > kmin) ? ex2(ti_prob_log2(p, v[i], m_use)) : 0.f;
                             l_run += v[i];
                         }
                     }
@@ -444,7 +445,7 @@ TI_API int ti_attention_prefill_tc_sink_bf16(void* out, const void* q, const voi
                                              int page_size, int num_pages, float scale, int window, int halves, int splits,
                                              int split_keys, float* scratch, long long scratch_floats, int has_sink, float sink,
                                              float out_scale, const float* head_sinks, const void* gate, int ld_gate,
-                                             int gate_off, int* status, cudaStream_t stream) {
+                                             int gate_off, float softcap, int* status, cudaStream_t stream) {
     TI_REQUIRE(splits >= 1 && splits <= 65535, "attention_prefill_tc: %d shares of the keys", splits);
     TI_REQUIRE(splits == 1 || (split_keys > 0 && split_keys % KT == 0 && scratch != nullptr &&
                                scratch_floats >= ti_attention_prefill_scratch_floats(num_tiles, halves, splits, hq, d)),
@@ -463,6 +464,7 @@ TI_API int ti_attention_prefill_tc_sink_bf16(void* out, const void* q, const voi
     p.out = (__nv_bfloat16*)out; p.tiles = tiles; p.block_table = block_table; p.max_blocks = max_blocks;
     p.hq = hq; p.hkv = hkv; p.page_size = page_size; p.num_pages = num_pages; p.window = window;
     p.scale_log2 = scale * 1.4426950408889634f; p.status = status; p.halves = halves ? 1 : 0;
+    TI_SET_SCORE_CAP(p, scale, softcap);
     p.has_sink = has_sink || head_sinks ? 1 : 0; p.sink_log2 = sink * 1.4426950408889634f; p.out_scale = out_scale;
     p.head_sinks = head_sinks; p.gate = (const __nv_bfloat16*)gate; p.ld_gate = ld_gate; p.gate_off = gate_off;
     const int slots = halves ? 2 * num_tiles : num_tiles;
@@ -502,5 +504,5 @@ TI_API int ti_attention_prefill_tc_bf16(void* out, const void* q, const void* kv
                                         cudaStream_t stream) {
     return ti_attention_prefill_tc_sink_bf16(out, q, kv_cache, tiles, num_tiles, num_tokens, block_table, max_blocks, hq, hkv, d,
                                              page_size, num_pages, scale, window, halves, splits, split_keys, scratch,
-                                             scratch_floats, 0, 0.f, 1.f, nullptr, nullptr, 0, 0, status, stream);
+                                             scratch_floats, 0, 0.f, 1.f, nullptr, nullptr, 0, 0, 0.f, status, stream);
 }

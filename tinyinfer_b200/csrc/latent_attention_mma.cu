@@ -41,6 +41,7 @@ struct Args {
     const int *positions, *token_seq, *cu_seqlens, *block_table;
     int max_blocks, num_seqs, num_tokens, heads, rank, rot, page_size, num_pages;
     float scale;
+    int window;                    // 0: every key up to the query's own; n: the last n (itself included)
     int splits, tpb, hpb, dkp;
     int* status;
 };
@@ -113,11 +114,12 @@ __global__ void __launch_bounds__(128 * MW, PER_SM) latent_attend_mma_kernel(Arg
             *reinterpret_cast<uint2*>(Qs + r * lds + c) = make_uint2(pack_bf16(v.x, v.y), pack_bf16(v.z, v.w));
         }
     }
-    const int hi = a.positions[tok0 + ntok - 1];              // the block's last token sees the most keys
-    int first_key = 0, last_key = hi + 1;
+    const int hi = a.positions[tok0 + ntok - 1];              // the block's last token sees the most keys,
+    const int lo = a.window > 0 ? max(0, a.positions[tok0] - a.window + 1) : 0;      // its first the oldest
+    int first_key = lo, last_key = hi + 1;
     if (a.splits > 1) {
-        const int per = ((hi + 1 + a.splits - 1) / a.splits + KEYS - 1) / KEYS * KEYS;
-        first_key = blockIdx.z * per;
+        const int per = ((hi + 1 - lo + a.splits - 1) / a.splits + KEYS - 1) / KEYS * KEYS;
+        first_key = lo + blockIdx.z * per;
         last_key = min(hi + 1, first_key + per);
     }
     const int* table = a.block_table + (size_t)seq * a.max_blocks;
@@ -156,6 +158,8 @@ __global__ void __launch_bounds__(128 * MW, PER_SM) latent_attend_mma_kernel(Arg
         for (int e = 0; e < 4; ++e) o[nt][e] = 0.f;
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
     const int pos_a = row_pos[mw * 16 + g], pos_b = row_pos[mw * 16 + g + 8];
+    // a row sees the keys (old, pos]: old = pos - window, or before the first key without a window
+    const int old_a = a.window > 0 ? pos_a - a.window : -1, old_b = a.window > 0 ? pos_b - a.window : -1;
     const int ksteps = dkp / 64;                               // k steps of 16 in this warp's quarter of the features
     const __nv_bfloat16* q_base = Qs + (mw * 16 + (lane & 15)) * lds + nw * (dkp / 4) + (lane >> 4) * 8;
     float* s_mine = Ss + ((mw * 4 + nw) * 16) * SPAD;
@@ -212,10 +216,10 @@ __global__ void __launch_bounds__(128 * MW, PER_SM) latent_attend_mma_kernel(Arg
                 ra.x += xa.x; ra.y += xa.y; rb.x += xb.x; rb.y += xb.y;
             }
             const int key = j0 + ni * 8 + t4 * 2;
-            p[ni][0] = (key < last_key && key <= pos_a) ? ra.x * a.scale : -INFINITY;
-            p[ni][1] = (key + 1 < last_key && key + 1 <= pos_a) ? ra.y * a.scale : -INFINITY;
-            p[ni][2] = (key < last_key && key <= pos_b) ? rb.x * a.scale : -INFINITY;
-            p[ni][3] = (key + 1 < last_key && key + 1 <= pos_b) ? rb.y * a.scale : -INFINITY;
+            p[ni][0] = (key < last_key && key <= pos_a && key > old_a) ? ra.x * a.scale : -INFINITY;
+            p[ni][1] = (key + 1 < last_key && key + 1 <= pos_a && key + 1 > old_a) ? ra.y * a.scale : -INFINITY;
+            p[ni][2] = (key < last_key && key <= pos_b && key > old_b) ? rb.x * a.scale : -INFINITY;
+            p[ni][3] = (key + 1 < last_key && key + 1 <= pos_b && key + 1 > old_b) ? rb.y * a.scale : -INFINITY;
         }
         float corr[2];
 #pragma unroll
@@ -317,9 +321,9 @@ TI_API int ti_latent_attend_mma_ok(int rank, int rot) { return (rank + rot) % 8 
 TI_API int ti_latent_attend_mma(void* out, float* parts, long long parts_floats, const float* q, const void* cache,
                                 const float* sink, const int* positions, const int* token_seq, const int* cu_seqlens,
                                 const int* block_table, int max_blocks, int num_seqs, int num_tokens, int heads, int rank,
-                                int rot, int page_size, int num_pages, float scale, int splits, int decode, int* status,
-                                cudaStream_t stream) {
-    TI_REQUIRE(num_tokens >= 0 && heads > 0 && rank > 0 && rot >= 0 && page_size > 0 && num_seqs > 0, "latent_attend_mma: bad sizes");
+                                int rot, int page_size, int num_pages, float scale, int window, int splits, int decode,
+                                int* status, cudaStream_t stream) {
+    TI_REQUIRE(num_tokens >= 0 && heads > 0 && rank > 0 && rot >= 0 && page_size > 0 && num_seqs > 0 && window >= 0, "latent_attend_mma: bad sizes");
     TI_REQUIRE(ti_latent_attend_mma_ok(rank, rot), "latent_attend_mma: rows of %d + %d features are not taken", rank, rot);
     TI_REQUIRE(splits >= 1 && splits <= 65535, "latent_attend_mma: bad number of splits");
     TI_REQUIRE(splits == 1 || (parts != nullptr && parts_floats >= (long long)num_tokens * heads * splits * (rank + 2)),
@@ -331,7 +335,7 @@ TI_API int ti_latent_attend_mma(void* out, float* parts, long long parts_floats,
     a.out = (__nv_bfloat16*)out; a.parts = parts; a.q = q; a.cache = (const __nv_bfloat16*)cache; a.sink = sink;
     a.positions = positions; a.token_seq = token_seq; a.cu_seqlens = cu_seqlens; a.block_table = block_table;
     a.max_blocks = max_blocks; a.num_seqs = num_seqs; a.num_tokens = num_tokens; a.heads = heads; a.rank = rank; a.rot = rot;
-    a.page_size = page_size; a.num_pages = num_pages; a.scale = scale; a.splits = splits; a.status = status;
+    a.page_size = page_size; a.num_pages = num_pages; a.scale = scale; a.window = window; a.splits = splits; a.status = status;
     a.hpb = heads < rows ? heads : rows;
     a.tpb = decode ? 1 : (rows / a.hpb > 0 ? rows / a.hpb : 1);
     const int nt = rank <= 128 ? 4 : (rank <= 256 ? 8 : 16);

@@ -64,7 +64,7 @@ _SIGNATURES = {
         "ti_latent_merge": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
         "ti_latent_attend_mma_ok": [c_int, c_int],
         "ti_latent_attend_mma": [c_void_p, c_void_p, c_ll, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                                 c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int,
+                                 c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int,
                                  c_void_p, c_void_p],
         "ti_causal_conv": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                            c_int, c_int, c_int, c_int, c_void_p],
@@ -149,14 +149,14 @@ _SIGNATURES["sm100"]["ti_attention_decode_bf16"] = [
 _SIGNATURES["sm100"]["ti_attention_decode_sink_bf16"] = [
     c_void_p, c_void_p, c_void_p, c_void_p, c_ll, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
     c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_float, c_float, c_void_p, c_void_p, c_int, c_int,
-    c_void_p, c_void_p]
+    c_float, c_void_p, c_void_p]
 _SIGNATURES["sm100"]["ti_attention_prefill_pair_sink_bf16"] = [
     c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
-    c_float, c_int, c_int, c_float, c_float, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]
+    c_float, c_int, c_int, c_float, c_float, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p, c_void_p]
 _SIGNATURES["sm100"]["ti_attention_prefill_tc_sink_bf16"] = [
     c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
     c_float, c_int, c_int, c_int, c_int, c_void_p, c_ll, c_int, c_float, c_float, c_void_p, c_void_p, c_int, c_int,
-    c_void_p, c_void_p]
+    c_float, c_void_p, c_void_p]
 _SIGNATURES["sm100"]["ti_attention_decode_scratch_floats"] = [c_int, c_int, c_int, c_int, c_int, c_int]
 _SIGNATURES["sm100"]["ti_attention_prefill_pair_bf16"] = [
     c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
@@ -665,9 +665,9 @@ def paged_attention(q: torch.Tensor, kv_cache: torch.Tensor, *, positions: torch
         return out
     has_sink, sink_v = int(sink is not None), float(sink or 0.0)
     _check_head_extras(q, head_sinks, gate, gate_offset)
-    extras = (_ptr(head_sinks), _ptr(gate), gate.shape[1] if gate is not None else 0, int(gate_offset))
-    if softcap or not attention_tensor_cores_ok(q, kv_cache):
-        if q.dtype == torch.bfloat16 and not attention_tensor_cores_ok(q, kv_cache):
+    extras = (_ptr(head_sinks), _ptr(gate), gate.shape[1] if gate is not None else 0, int(gate_offset), float(softcap or 0.0))
+    if not attention_tensor_cores_ok(q, kv_cache):
+        if q.dtype == torch.bfloat16:
             _warn_generic_attention(hq, hkv, d, page_size)
         if softcap or has_sink or out_scale != 1.0 or head_sinks is not None or gate is not None:
             return attention_rows(q, kv_cache, v_dim=d, positions=positions, token_seq=token_seq, block_table=block_table,
@@ -903,8 +903,8 @@ def latent_attention(q_rows: torch.Tensor, cache: torch.Tensor, *, heads: int, r
     in the cache's dtype. ``sink`` float32 [heads]: exp(sink) joins every softmax denominator. ``max_context``
     (a host number, the longest context of the step) only decides over how many blocks the keys are shared.
     ``step`` (the StepContext): with it a bfloat16 cache whose rows are a multiple of 8 features runs on the
-    tensor cores, prompt portions and decoded tokens in their own forms; without it, in float32 or with a window,
-    the float32-arithmetic kernel runs."""
+    tensor cores, prompt portions and decoded tokens in their own forms; without it, or in float32, the
+    float32-arithmetic kernel runs. ``window``: a query sees only the last so many keys, itself included."""
     _check(q_rows, "q_rows", torch.float32, 2)
     _check(cache, "cache", None, 5)
     _check(positions, "positions", torch.int32, 1)
@@ -921,9 +921,11 @@ def latent_attention(q_rows: torch.Tensor, cache: torch.Tensor, *, heads: int, r
     if t == 0:
         return out
 
+    reach = min(int(max_context), int(window)) if window else int(max_context)     # keys a query can see at most
+
     def share_out(blocks: int, least: int = LATENT_SPLIT_MIN_KEYS) -> int:
-        if blocks < LATENT_TARGET_BLOCKS and max_context >= 2 * least:
-            return max(1, min(-(-LATENT_TARGET_BLOCKS // blocks), int(max_context) // least, 64))
+        if blocks < LATENT_TARGET_BLOCKS and reach >= 2 * least:
+            return max(1, min(-(-LATENT_TARGET_BLOCKS // blocks), reach // least, 64))
         return 1
 
     def scratch(splits: int):
@@ -932,7 +934,7 @@ def latent_attention(q_rows: torch.Tensor, cache: torch.Tensor, *, heads: int, r
         parts = _decode_scratch(cache.device, t * heads * splits * (rank + 2))
         return parts, parts.numel()
 
-    if (step is not None and cache.dtype == torch.bfloat16 and not window
+    if (step is not None and cache.dtype == torch.bfloat16
             and int(_fn("latent", "ti_latent_attend_mma_ok")(rank, rot))):
         decode = step.max_q_len == 1
         rows = 16 if decode else 32
@@ -942,8 +944,8 @@ def latent_attention(q_rows: torch.Tensor, cache: torch.Tensor, *, heads: int, r
         parts, parts_floats = scratch(splits)
         _run("latent", "ti_latent_attend_mma", out.data_ptr(), _ptr(parts), parts_floats, q_rows.data_ptr(), cache.data_ptr(),
              _ptr(sink), positions.data_ptr(), token_seq.data_ptr(), step.cu_seqlens.data_ptr(), block_table.data_ptr(),
-             block_table.shape[1], step.num_seqs, t, heads, rank, rot, cache.shape[3], cache.shape[1], float(scale), splits,
-             int(decode), _ptr(status), _stream())
+             block_table.shape[1], step.num_seqs, t, heads, rank, rot, cache.shape[3], cache.shape[1], float(scale),
+             int(window or 0), splits, int(decode), _ptr(status), _stream())
         if splits > 1:
             _run("latent", "ti_latent_merge", out.data_ptr(), parts.data_ptr(), _ptr(sink), t, heads, rank, splits,
                  _dtype_code(cache), _stream())
