@@ -25,6 +25,9 @@ the layer sizes of real models, each beside the Qwen3 preset of the same width a
 linear attention, state-space layers, several residual streams), and ``--design sinulix`` for the Sinulix design
 (attention with head sinks and gates, retention, the channel-wise delta rule, clamped-GLU experts), which also runs
 the Ravutar preset of the same width, the nearest design with matrix-state layers, for the kernel-by-kernel comparison.
+``--design fezozen`` does it for the Fezozen design (capped, windowed and latent attention, sigmoid-scored experts
+weighted at their input, a norm before and after every sublayer), beside Qwen3 and the Gulisun preset of the same
+width, the nearest design with latent attention and routed experts around a float32 stream.
 
 ``--impl reference`` runs the unmodified reference project from ``baseline/_ref`` through its own
 public API (``tinyinfer.LLM(Config(...))``, ``add_request``, ``step``) on a model folder of the same
@@ -616,12 +619,60 @@ def sinulix_numbers(cfg, batch, context):
     return dict(macs=macs, attn_per_key=attn_per_key, head=head, step_bytes=step_bytes, scan_flops=scan_flops)
 
 
+def fezozen_numbers(cfg, batch, context):
+    """As ``gulisun_numbers`` for the Fezozen design: matrix elements a token multiplies (active experts only; the
+    latent attention's per-head key and value maps included), attention flops per key, where a key counts only while
+    a layer's window holds it (``attn_window_keys``: per layer the flops a key costs and the window, for the prompt's
+    sum), and the bytes a decode step must move: dense weights, the experts a batch of this size is expected to touch,
+    the head, and of every layer's cache the rows its window keeps. A layer that runs another layer's tensors reads
+    them again (they do not stay in the 126 MB of L2 between the two runs), so every run counts."""
+    w, macs, dense, expert_bytes, cache_bytes, per_layer = cfg.width, 0, 0, 0.0, 0.0, []
+    for layer in cfg.layers:
+        m, f = layer["mixer"], layer.get("mlp")
+        window = (m.get("mask") or {}).get("size") or 0
+        seen = min(context, window) if window else context
+        if layer["type"] == "latent_attention":
+            h, d, r, v, kr = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
+            part = w * h * (d + r) + (kr + r) * w + h * d * kr + h * v * kr + 2 * w * h * v
+            per_layer.append((2.0 * h * (kr + r) + 2.0 * h * kr, window))
+            cache_bytes += seen * (kr + r) * 2
+        else:
+            h, g, d, v = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+            part = w * (h * d + g * (d + v)) + w * h * v
+            per_layer.append((2.0 * h * (d + v), window))
+            cache_bytes += seen * g * (d + v) * 2
+        macs += part
+        dense += part
+        if f is not None:
+            e, top, ff = f["router"]["experts"], f["router"]["top"], f["expert"]["ff"]
+            macs += top * 3 * ff * w + e * w
+            dense += e * w
+            touched = e * (1.0 - (1.0 - top / e) ** batch)
+            expert_bytes += touched * 3 * ff * w * 2
+    head = cfg.vocab * w
+    step_bytes = dense * 2 + expert_bytes + head * 2 + batch * cache_bytes
+    return dict(macs=macs, attn_per_key=0.0, attn_window_keys=per_layer, head=head, step_bytes=step_bytes)
+
+
+def windowed_attention_flops(per_layer, t):
+    """Attention flops of a prompt of ``t`` tokens: position p sees min(p + 1, window) keys of a layer."""
+    total = 0.0
+    for per_key, window in per_layer:
+        if window and window < t:
+            total += per_key * (window * (window + 1) / 2.0 + (t - window) * window)
+        else:
+            total += per_key * t * (t + 1) / 2.0
+    return total
+
+
 DESIGNS = {      # design -> (what its numbers are made with, [(its preset, the Qwen3 preset of the same width)])
+    "fezozen": (fezozen_numbers, (("fezozen-1b", "0.6b"), ("fezozen-2b", "1.7b"))),
     "gulisun": (gulisun_numbers, (("gulisun-1b", "0.6b"), ("gulisun-2b", "1.7b"))),
     "ravutar": (ravutar_numbers, (("ravutar-1b", "0.6b"), ("ravutar-2b", "1.7b"))),
     "sinulix": (sinulix_numbers, (("sinulix-1b", "0.6b"), ("sinulix-2b", "1.7b"))),
 }
-SIBLINGS = {"sinulix-1b": ("ravutar", "ravutar-1b"), "sinulix-2b": ("ravutar", "ravutar-2b")}   # also measured beside it
+SIBLINGS = {"sinulix-1b": ("ravutar", "ravutar-1b"), "sinulix-2b": ("ravutar", "ravutar-2b"),   # also measured beside it
+            "fezozen-1b": ("gulisun", "gulisun-1b"), "fezozen-2b": ("gulisun", "gulisun-2b")}
 
 
 
@@ -693,7 +744,7 @@ def design_comparison(args) -> int:
         numbers = numbers_of(g, batch, context)
         t = prefill_tokens
         flops = (2.0 * numbers["macs"] * t + numbers["attn_per_key"] * t * (t + 1) / 2.0 + 2.0 * numbers["head"]
-                 + numbers.get("scan_flops", 0.0) * t)
+                 + numbers.get("scan_flops", 0.0) * t + windowed_attention_flops(numbers.get("attn_window_keys", ()), t))
         row = {"layers": layers, design: measure_design(g, peaks, flops, numbers["step_bytes"], batch, context, steps,
                                                            warmup, prefill_tokens)}
         q = preset_config(theirs, num_hidden_layers=layers)
@@ -735,7 +786,7 @@ def main() -> int:
     ap.add_argument("--skip-points", action="store_true", help="only the headline batch")
     ap.add_argument("--skip-extras", action="store_true", help="leave out the 'configs' of the line")
     ap.add_argument("--extras", default="32b,mix,cpu", help="which of the other configurations to run")
-    ap.add_argument("--design", default="", choices=["", "gulisun", "ravutar", "sinulix"],
+    ap.add_argument("--design", default="", choices=["", "gulisun", "ravutar", "sinulix", "fezozen"],
                     help="instead of the headline: prefill and decode of this design beside Qwen3 at equal size")
     ap.add_argument("--ref-block-size", type=int, default=256, help="reference arm: its kvcache_block_size (its default)")
     ap.add_argument("--ref-step-tokens", type=int, default=32,
