@@ -220,7 +220,7 @@ struct RunWalk {
 // two CTAs of 8 or 9 query heads a kv head (head size 128) share an SM (32 requests x 8,192 keys, 64 query heads
 // over 8: 193 -> 170 us); with fewer query heads, where two CTAs fit anyway, the whole buffer's merge is shorter
 // (8 x 4,096 keys, 32 over 8: 26.9 us against 30.0).
-template <int D, int NS, bool SLIM>
+template <int D, int NS, bool SLIM, bool CAP>
 __global__ void __launch_bounds__(THREADS) decode_attention_kernel(const __grid_constant__ CUtensorMap kv_map,
                                                                    const AttnParams p) {
     using S = Smem<D>;
@@ -347,7 +347,7 @@ __global__ void __launch_bounds__(THREADS) decode_attention_kernel(const __grid_
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         const int tok = tok0 + nb * 8 + c + (j & 1);
-                        const float v = (tok >= k_begin && tok < k_end) ? ti_score_log2(p, sc[nb][j]) : -INFINITY;
+                        const float v = (tok >= k_begin && tok < k_end) ? ti_score_log2<CAP>(p, sc[nb][j]) : -INFINITY;
                         sc[nb][j] = v;
                         mx[j >> 1] = fmaxf(mx[j >> 1], v);
                     }
@@ -616,7 +616,7 @@ namespace {
 // is too. nullptr: no current device.
 int* configured_bytes(int which) {
     constexpr int MAX_DEVICES = 64;
-    static int bytes[4][MAX_DEVICES] = {};
+    static int bytes[8][MAX_DEVICES] = {};
     int dev = -1;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEVICES) return nullptr;
     return &bytes[which][dev];
@@ -696,39 +696,35 @@ TI_API int ti_attention_decode_sink_bf16(void* out, const void* q, const void* k
     p.has_sink = has_sink || head_sinks ? 1 : 0; p.sink_log2 = sink * 1.4426950408889634f; p.out_scale = out_scale;
     p.head_sinks = head_sinks; p.gate = (const __nv_bfloat16*)gate; p.ld_gate = ld_gate; p.gate_off = gate_off;
     p.num_rows = num_rows; p.num_ctas = ctas;
+    // which: the record of configured_bytes; a capped kernel is another function and keeps a record of its own
+#define DEC_GO(D, NS, SLIM, CAP, which, bytes_expr)                                                                        \
+    do {                                                                                                                   \
+        const int bytes = (bytes_expr);                                                                                    \
+        int* configured = configured_bytes((which) + ((CAP) ? 4 : 0));                                                     \
+        TI_REQUIRE(configured != nullptr, "attention_decode: no current device");                                          \
+        if (*configured < bytes) {                                                                                         \
+            if (set_smem(decode_attention_kernel<D, NS, SLIM, CAP>, bytes, "attention_decode")) return -1;                 \
+            *configured = bytes;                                                                                           \
+        }                                                                                                                  \
+        ti_launch(decode_attention_kernel<D, NS, SLIM, CAP>, ctas, THREADS, bytes, stream, map, p);                        \
+        TI_CHECK_LAUNCH("attention_decode");                                                                               \
+        ti_launch(decode_merge_kernel<D>, dim3(num_rows, hq), D, 0, stream, p);                                            \
+    } while (0)
+    const bool capped = p.cap_log2 > 0.f;
     if (d == 128 && decode_form(group) == 2) {
-        const int bytes = Smem<128>::decode_bytes(group, 2 * STAGES);
-        int* configured = configured_bytes(2);
-        TI_REQUIRE(configured != nullptr, "attention_decode: no current device");
-        if (*configured < bytes) { if (set_smem(decode_attention_kernel<128, 2 * STAGES, false>, bytes, "attention_decode")) return -1; *configured = bytes; }
-        ti_launch(decode_attention_kernel<128, 2 * STAGES, false>, ctas, THREADS, bytes, stream, map, p);
-        TI_CHECK_LAUNCH("attention_decode");
-        ti_launch(decode_merge_kernel<128>, dim3(num_rows, hq), 128, 0, stream, p);
+        if (capped) DEC_GO(128, 2 * STAGES, false, true, 2, Smem<128>::decode_bytes(group, 2 * STAGES));
+        else DEC_GO(128, 2 * STAGES, false, false, 2, Smem<128>::decode_bytes(group, 2 * STAGES));
     } else if (d == 128 && decode_form(group) == 1) {
-        const int bytes = Smem<128>::decode_bytes(group, STAGES, true);
-        int* configured = configured_bytes(3);
-        TI_REQUIRE(configured != nullptr, "attention_decode: no current device");
-        if (*configured < bytes) { if (set_smem(decode_attention_kernel<128, STAGES, true>, bytes, "attention_decode")) return -1; *configured = bytes; }
-        ti_launch(decode_attention_kernel<128, STAGES, true>, ctas, THREADS, bytes, stream, map, p);
-        TI_CHECK_LAUNCH("attention_decode");
-        ti_launch(decode_merge_kernel<128>, dim3(num_rows, hq), 128, 0, stream, p);
+        if (capped) DEC_GO(128, STAGES, true, true, 3, Smem<128>::decode_bytes(group, STAGES, true));
+        else DEC_GO(128, STAGES, true, false, 3, Smem<128>::decode_bytes(group, STAGES, true));
     } else if (d == 128) {
-        const int bytes = Smem<128>::decode_bytes(group);
-        int* configured = configured_bytes(0);
-        TI_REQUIRE(configured != nullptr, "attention_decode: no current device");
-        if (*configured < bytes) { if (set_smem(decode_attention_kernel<128, STAGES, false>, bytes, "attention_decode")) return -1; *configured = bytes; }
-        ti_launch(decode_attention_kernel<128, STAGES, false>, ctas, THREADS, bytes, stream, map, p);
-        TI_CHECK_LAUNCH("attention_decode");
-        ti_launch(decode_merge_kernel<128>, dim3(num_rows, hq), 128, 0, stream, p);
+        if (capped) DEC_GO(128, STAGES, false, true, 0, Smem<128>::decode_bytes(group));
+        else DEC_GO(128, STAGES, false, false, 0, Smem<128>::decode_bytes(group));
     } else {
-        const int bytes = Smem<64>::decode_bytes(group);
-        int* configured = configured_bytes(1);
-        TI_REQUIRE(configured != nullptr, "attention_decode: no current device");
-        if (*configured < bytes) { if (set_smem(decode_attention_kernel<64, STAGES, false>, bytes, "attention_decode")) return -1; *configured = bytes; }
-        ti_launch(decode_attention_kernel<64, STAGES, false>, ctas, THREADS, bytes, stream, map, p);
-        TI_CHECK_LAUNCH("attention_decode");
-        ti_launch(decode_merge_kernel<64>, dim3(num_rows, hq), 64, 0, stream, p);
+        if (capped) DEC_GO(64, STAGES, false, true, 1, Smem<64>::decode_bytes(group));
+        else DEC_GO(64, STAGES, false, false, 1, Smem<64>::decode_bytes(group));
     }
+#undef DEC_GO
     TI_CHECK_LAUNCH("attention_decode_merge");
     return 0;
 }

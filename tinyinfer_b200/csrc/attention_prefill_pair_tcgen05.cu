@@ -121,7 +121,7 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t* r) {
 }
 __device__ __forceinline__ void tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
-template <int D>
+template <int D, bool CAP>
 __global__ void __launch_bounds__(PP_THREADS, 1)
 prefill_attention_pair_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap kv_map,
                               const PairParams p) {
@@ -338,7 +338,7 @@ prefill_attention_pair_kernel(const __grid_constant__ CUtensorMap q_map, const _
                     m4[k & 3] = fmaxf(m4[k & 3], __uint_as_float(sr[k]));
                 }
             }
-            const float mx = ti_score_log2(p, fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])));   // the scale is positive, a cap rises with the score
+            const float mx = ti_score_log2<CAP>(p, fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3])));   // the scale is positive, a cap rises with the score
             // The reference maximum moves only when the row's maximum has outgrown it by RESCALE_STEP.
             const bool move = mx > m_ref + RESCALE_STEP || (m_ref == -INFINITY && mx > -INFINITY);
             const float m_new = move ? mx : m_ref;
@@ -354,7 +354,7 @@ prefill_attention_pair_kernel(const __grid_constant__ CUtensorMap q_map, const _
             for (int k0 = 0; k0 < KT; k0 += 16) {
 #pragma unroll
                 for (int u = 0; u < 16; ++u)
-                    sr[k0 + u] = __float_as_uint(ex2(ti_prob_log2(p, __uint_as_float(sr[k0 + u]), m_use)));
+                    sr[k0 + u] = __float_as_uint(ex2(ti_prob_log2<CAP>(p, __uint_as_float(sr[k0 + u]), m_use)));
 #pragma unroll
                 for (int u = 0; u < 16; u += 2) {
                     const float a = __uint_as_float(sr[k0 + u]), b = __uint_as_float(sr[k0 + u + 1]);
@@ -467,23 +467,21 @@ TI_API int ti_attention_prefill_pair_sink_bf16(void* out, const void* q, const v
     p.has_sink = has_sink || head_sinks ? 1 : 0; p.sink_log2 = sink * 1.4426950408889634f; p.out_scale = out_scale;
     p.head_sinks = head_sinks; p.gate = (const __nv_bfloat16*)gate; p.ld_gate = ld_gate; p.gate_off = gate_off;
     dim3 grid(hq, num_tiles);
-    if (d == 128) {
-        static bool once = false;
-        if (!once) {
-            cudaError_t e = cudaFuncSetAttribute(prefill_attention_pair_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, PpSmem<128>::BYTES);
-            TI_REQUIRE(e == cudaSuccess, "attention_prefill_pair: shared memory: %s", cudaGetErrorString(e));
-            once = true;
-        }
-        ti_launch(prefill_attention_pair_kernel<128>, grid, PP_THREADS, PpSmem<128>::BYTES, stream, q_map, kv_map, p);
-    } else {
-        static bool once = false;
-        if (!once) {
-            cudaError_t e = cudaFuncSetAttribute(prefill_attention_pair_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, PpSmem<64>::BYTES);
-            TI_REQUIRE(e == cudaSuccess, "attention_prefill_pair: shared memory: %s", cudaGetErrorString(e));
-            once = true;
-        }
-        ti_launch(prefill_attention_pair_kernel<64>, grid, PP_THREADS, PpSmem<64>::BYTES, stream, q_map, kv_map, p);
-    }
+#define PP_GO(D, CAP)                                                                                                            \
+    do {                                                                                                                         \
+        static bool once = false;                                                                                                \
+        if (!once) {                                                                                                             \
+            cudaError_t e = cudaFuncSetAttribute(prefill_attention_pair_kernel<D, CAP>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                                 PpSmem<D>::BYTES);                                                              \
+            TI_REQUIRE(e == cudaSuccess, "attention_prefill_pair: shared memory: %s", cudaGetErrorString(e));                    \
+            once = true;                                                                                                         \
+        }                                                                                                                        \
+        ti_launch(prefill_attention_pair_kernel<D, CAP>, grid, PP_THREADS, PpSmem<D>::BYTES, stream, q_map, kv_map, p);          \
+    } while (0)
+    const bool capped = p.cap_log2 > 0.f;
+    if (d == 128) { if (capped) PP_GO(128, true); else PP_GO(128, false); }
+    else { if (capped) PP_GO(64, true); else PP_GO(64, false); }
+#undef PP_GO
     TI_CHECK_LAUNCH("attention_prefill_pair");
     return 0;
 }

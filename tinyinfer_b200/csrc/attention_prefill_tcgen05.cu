@@ -66,7 +66,7 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
-template <int D>
+template <int D, bool CAP>
 __global__ void __launch_bounds__(PF_THREADS, 1)
 prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap kv_map,
                             const PrefillParams p) {
@@ -271,7 +271,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
             max_xch[b][half][r] = mx;
             asm volatile("bar.sync %0, 64;" ::"r"(1 + lane_group) : "memory");     // the two warps of this row quarter
             mx = fmaxf(mx, max_xch[b][half ^ 1][r]);
-            const float m_new = fmaxf(m_run, ti_score_log2(p, mx));     // the cap rises with the score, like the scale
+            const float m_new = fmaxf(m_run, ti_score_log2<CAP>(p, mx));     // the cap rises with the score, like the scale
             const float m_use = m_new == -INFINITY ? 0.f : m_new;
             const float corr = ex2(m_run - m_use);
             m_run = m_new;
@@ -312,13 +312,13 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __g
                     if (c + 31 <= wmax0 && c > wmin1) {
 #pragma unroll
                         for (int i = 0; i < 32; ++i) {
-                            v[i] = ex2(ti_prob_log2(p, v[i], m_use));
+                            v[i] = ex2(ti_prob_log2<CAP>(p, v[i], m_use));
                             l_run += v[i];
                         }
                     } else {
 #pragma unroll
                         for (int i = 0; i < 32; ++i) {
-                            v[i] = (c + i <= kmax && c + i > kmin) ? ex2(ti_prob_log2(p, v[i], m_use)) : 0.f;
+                            v[i] = (c + i <= kmax && c + i > kmin) ? ex2(ti_prob_log2<CAP>(p, v[i], m_use)) : 0.f;
                             l_run += v[i];
                         }
                     }
@@ -471,23 +471,21 @@ TI_API int ti_attention_prefill_tc_sink_bf16(void* out, const void* q, const voi
     p.splits = splits; p.split_keys = split_keys;
     p.part_o = scratch; p.part_ml = scratch ? scratch + (long long)slots * splits * hq * QM * d : nullptr;
     dim3 grid(hq, slots, splits);
-    if (d == 128) {
-        static bool once = false;
-        if (!once) {
-            cudaError_t e = cudaFuncSetAttribute(prefill_attention_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, PfSmem<128>::BYTES);
-            TI_REQUIRE(e == cudaSuccess, "attention_prefill_tc: shared memory: %s", cudaGetErrorString(e));
-            once = true;
-        }
-        ti_launch(prefill_attention_tc_kernel<128>, grid, PF_THREADS, PfSmem<128>::BYTES, stream, q_map, kv_map, p);
-    } else {
-        static bool once = false;
-        if (!once) {
-            cudaError_t e = cudaFuncSetAttribute(prefill_attention_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, PfSmem<64>::BYTES);
-            TI_REQUIRE(e == cudaSuccess, "attention_prefill_tc: shared memory: %s", cudaGetErrorString(e));
-            once = true;
-        }
-        ti_launch(prefill_attention_tc_kernel<64>, grid, PF_THREADS, PfSmem<64>::BYTES, stream, q_map, kv_map, p);
-    }
+#define PF_GO(D, CAP)                                                                                                          \
+    do {                                                                                                                       \
+        static bool once = false;                                                                                              \
+        if (!once) {                                                                                                           \
+            cudaError_t e = cudaFuncSetAttribute(prefill_attention_tc_kernel<D, CAP>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                                 PfSmem<D>::BYTES);                                                            \
+            TI_REQUIRE(e == cudaSuccess, "attention_prefill_tc: shared memory: %s", cudaGetErrorString(e));                    \
+            once = true;                                                                                                       \
+        }                                                                                                                      \
+        ti_launch(prefill_attention_tc_kernel<D, CAP>, grid, PF_THREADS, PfSmem<D>::BYTES, stream, q_map, kv_map, p);          \
+    } while (0)
+    const bool capped = p.cap_log2 > 0.f;
+    if (d == 128) { if (capped) PF_GO(128, true); else PF_GO(128, false); }
+    else { if (capped) PF_GO(64, true); else PF_GO(64, false); }
+#undef PF_GO
     TI_CHECK_LAUNCH("attention_prefill_tc");
     if (splits > 1) {
         if (d == 128) ti_launch(prefill_merge_kernel<128>, dim3(slots * QM, hq), 128, 0, stream, p);

@@ -125,24 +125,34 @@ __device__ __forceinline__ float block_max(float v, float* red) {
 }
 
 // Scores that level off smoothly: s -> cap * tanh(s / cap). P is an attention kernel's parameter block with scale_log2
-// (the softmax scale times log2 e), cap_log2 (cap * log2 e; 0: no cap) and cap_arg (2 log2 e * scale / cap). The result is
-// in log2 units, like raw * scale_log2. tanh(x) = 1 - 2 / (2^(2 x log2 e) + 1); a masked score (-inf) stays -inf.
-template <typename P> __device__ __forceinline__ float ti_score_log2(const P& p, float raw) {
-    if (p.cap_log2 > 0.f) {
+// (the softmax scale times log2 e), cap_log2 (cap * log2 e; 0: no cap) and cap_arg (scale / cap). The result is in log2
+// units, like raw * scale_log2; a masked score (-inf) stays -inf. These are the bfloat16 tensor-core kernels, whose
+// softmax is bound by the transcendental unit: the tanh is the unit's own instruction (one more trip a score, relative
+// error 2^-11, below the rounding of the bfloat16 probabilities); from an exponential and a division it was three trips
+// a score and the prompt kernel 2.5 times its uncapped time.
+// CAP is a template parameter of the kernels, so that the kernels of models without a cap are the code they were.
+__device__ __forceinline__ float ti_tanh_approx(float x) {
+    float y;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+template <bool CAP, typename P> __device__ __forceinline__ float ti_score_log2(const P& p, float raw) {
+    if constexpr (CAP) {
         if (raw == -INFINITY) return -INFINITY;
-        return p.cap_log2 * (1.f - __fdividef(2.f, exp2f(raw * p.cap_arg) + 1.f));
+        return p.cap_log2 * ti_tanh_approx(raw * p.cap_arg);
+    } else {
+        return raw * p.scale_log2;
     }
-    return raw * p.scale_log2;
 }
 // The exponent of a probability, score - m_use, in log2 units.
-template <typename P> __device__ __forceinline__ float ti_prob_log2(const P& p, float raw, float m_use) {
-    if (p.cap_log2 > 0.f) return ti_score_log2(p, raw) - m_use;
-    return fmaf(raw, p.scale_log2, -m_use);
+template <bool CAP, typename P> __device__ __forceinline__ float ti_prob_log2(const P& p, float raw, float m_use) {
+    if constexpr (CAP) return ti_score_log2<true>(p, raw) - m_use;
+    else return fmaf(raw, p.scale_log2, -m_use);
 }
 #define TI_SET_SCORE_CAP(p, scale, softcap)                                                        \
     do {                                                                                           \
         (p).cap_log2 = (softcap) > 0.f ? (softcap) * 1.4426950408889634f : 0.f;                     \
-        (p).cap_arg = (softcap) > 0.f ? 2.f * 1.4426950408889634f * (scale) / (softcap) : 0.f;      \
+        (p).cap_arg = (softcap) > 0.f ? (scale) / (softcap) : 0.f;                                  \
     } while (0)
 
 // A softmax sink and an output factor that may differ from head to head. P is an attention kernel's parameter block with
