@@ -229,9 +229,9 @@ def test_latent_attention_behind_a_window(heads, rank, rot, page, window, work, 
                                                          (4, 2, 128, 128, 1000)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_experts_scored_by_sigmoids_and_weighted_at_their_input(experts, top, ff, width, tokens, dtype):
-    """Sigmoid scores, the largest chosen, the score times the token's row as the expert's input, silu(gate) * up, the
-    plain sum of the outputs: op by op as the experts' part strings them together, in every form of the grouped
-    products that the token counts reach."""
+    """Sigmoid scores, the largest chosen, the score times the token's row as the expert's input (which the engine
+    applies behind the linear up product, inside the activation kernel), silu(gate) * up, the plain sum of the outputs: op
+    by op as the experts' part strings them together, in every form of the grouped products that the token counts reach."""
     from tinyinfer_b200 import ops
     gen = torch.Generator().manual_seed(experts * 7 + top)
     x = torch.randn(tokens, width, generator=gen).to(dtype)
@@ -249,19 +249,17 @@ def test_experts_scored_by_sigmoids_and_weighted_at_their_input(experts, top, ff
     assert torch.equal(torch.sort(got_chosen[clear], dim=-1).values, torch.sort(torch.topk(scores, top).indices[clear], dim=-1).values)
     assert (routing.weight.cpu().double() - torch.gather(scores, 1, got_chosen)).abs().max() < 1e-5
     assert float(routing.weight.sum(-1).max()) > 1.0 or top == 1        # sigmoids do not share one unit between them
-    gate_up = ops.expert_linear(xd, up.cuda(), routing, up=True, activation=False, weighted_input=True)
-    rows = ops.expert_linear(ops.silu_glu(gate_up), down.cuda(), routing, up=False)
+    assert torch.equal(routing.slot_weight.cpu()[routing.slot_of.cpu().long()], routing.weight.cpu())
+    gate_up = ops.expert_linear(xd, up.cuda(), routing, up=True, activation=False)
+    rows = ops.expert_linear(ops.silu_glu(gate_up, routing.slot_weight), down.cuda(), routing, up=False)
     got = ops.experts_combine(rows, xd, routing, experts, weighted=False).cpu().double()
     want = torch.zeros(tokens, width, dtype=torch.float64)
     for t in range(tokens):
         for c in range(top):
             e = int(got_chosen[t, c])
-            h = scores[t, e] * x[t].double()
-            if dtype == torch.bfloat16:
-                h = h.to(dtype).double()
-            gu = up[e].double() @ h
-            if dtype == torch.bfloat16:
-                gu = gu.to(dtype).double()
+            gu = up[e].double() @ (scores[t, e] * x[t].double())        # the expert reads its score times the row
+            if dtype == torch.bfloat16:      # the engine stores W h rounded and multiplies by the score behind it
+                gu = scores[t, e] * (gu / scores[t, e]).to(dtype).double()
             y = plain.silu(gu[:ff]) * gu[ff:]
             if dtype == torch.bfloat16:
                 y = y.to(dtype).double()

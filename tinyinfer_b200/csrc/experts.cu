@@ -1,6 +1,7 @@
 // A feed-forward made of many small experts, of which every token runs a few chosen by a router.
 //   route    : z = W_router x in float32 from the token's row (the float32 residual, or a sublayer's input in the
-//              compute dtype), s = softmax(z) over all experts (or, scoring 1, sigmoid(z) of each expert by itself), the `top` largest s + correction (a learned number per
+//              compute dtype), s = softmax(z) over all experts (or, scoring 1, sigmoid(z) of each expert by itself),
+//              the `top` largest s + correction (a learned number per
 //              expert that only steers the choice; first index on ties), weights s_k / (sum of the chosen + weight_eps)
 //              or, without renormalisation, s_k itself; also counts the tokens of every expert and gives each
 //              (token, choice) its rank among them. The last experts of the router may be identity experts, whose
@@ -16,10 +17,9 @@
 //   combine  : the same weighted sum alone, identity experts included, in the compute dtype
 //   clamped_glu : an expert's gated activation on the stored product [gate | up]: g = min(gate, limit),
 //              u = clamp(up, -limit, limit), g * sigmoid(alpha * g) * (u + 1)
-//   gather   : the tokens' rows in expert order, optionally each times the weight of its (token, choice): experts that
-//              are weighted at their INPUT (the activation between an expert's products is not linear, so the weight
-//              cannot move behind it)
-//   silu_glu : silu(gate) * up on the stored product [gate | up]
+//   silu_glu : silu(gate) * up on the stored product [gate | up]; optionally both halves of a row times the weight of its
+//              (token, choice) first: experts that are weighted at their INPUT. The up product is linear, so
+//              W (s h) = s (W h) and the weight rides in this kernel; the activation is not, so it cannot move further
 // A token's result depends on its own row alone: no capacity, nothing dropped, whatever else is in the batch.
 // Nothing here reads back to the host: grids are sized for the worst case and tiles beyond the plan's count return.
 #include "common.cuh"
@@ -156,7 +156,8 @@ __global__ void moe_plan_kernel(int* __restrict__ starts, int* __restrict__ tile
 }
 
 __global__ void moe_place_kernel(int* __restrict__ slot_of, int* __restrict__ token_of, const int* __restrict__ chosen,
-                                 const int* __restrict__ rank, const int* __restrict__ starts, int n, int top) {
+                                 const int* __restrict__ rank, const int* __restrict__ starts, int n, int top,
+                                 float* __restrict__ slot_weight, const float* __restrict__ weight) {
     ti_grid_launch_dependents();
     ti_grid_wait();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -164,16 +165,19 @@ __global__ void moe_place_kernel(int* __restrict__ slot_of, int* __restrict__ to
     const int slot = starts[chosen[i]] + rank[i];
     slot_of[i] = slot;
     token_of[slot] = i / top;
+    if (slot_weight) slot_weight[slot] = weight[i];        // the weights in expert order, for whoever works on sorted rows
 }
 
 // scoring 0: softmax over the experts; 1: the sigmoid of each logit.
+// slot_weight (float32 [tokens * top], or null): also receives every (token, choice)'s weight at its row in expert order.
 // counts (experts ints) must be zero on entry; the launcher clears them. x_dtype: of the tokens' rows (float32, or
 // the compute dtype of a sublayer's input); correction: float32 [experts] or null; renorm: the weights are divided by
 // their sum; real_experts: how many of the router's outputs are experts with weights (the rest: identity experts).
 TI_API int ti_moe_route(int* chosen, float* weight, int* rank, int* counts, int* starts, int* tiles, int* num_tiles,
                         int* slot_of, int* token_of, const void* x, const void* w_router, int num_tokens, int hidden,
                         int experts, int top, float weight_eps, const float* correction, int renorm, int real_experts,
-                        int tile_rows, int max_tiles, int scoring, int x_dtype, int dtype, cudaStream_t stream) {
+                        int tile_rows, int max_tiles, int scoring, float* slot_weight, int x_dtype, int dtype,
+                        cudaStream_t stream) {
     TI_REQUIRE(scoring == 0 || scoring == 1, "moe_route: scoring %d is neither the softmax (0) nor the sigmoid (1)", scoring);
     TI_REQUIRE(num_tokens >= 0 && hidden > 0 && experts > 0 && top > 0, "moe_route: bad sizes");
     TI_REQUIRE(top <= EX_MAX_TOP && top <= experts, "moe_route: top %d of %d experts (at most %d)", top, experts, EX_MAX_TOP);
@@ -198,7 +202,7 @@ TI_API int ti_moe_route(int* chosen, float* weight, int* rank, int* counts, int*
     TI_CHECK_LAUNCH("moe_plan");
     const int n = num_tokens * top;
     ti_launch(moe_place_kernel, (n + 127) / 128, 128, 0, stream, slot_of, token_of, (const int*)chosen, (const int*)rank,
-              (const int*)starts, n, top);
+              (const int*)starts, n, top, slot_weight, (const float*)weight);
     TI_CHECK_LAUNCH("moe_place");
     return 0;
 }
@@ -306,8 +310,7 @@ __global__ void __launch_bounds__(mt::THREADS) moe_gemm_mma_kernel(
 TI_API int ti_moe_tile_rows() { return EG_BM; }
 
 // up != 0: x [tokens, K] gathered through token_of, out [slots, N] in the compute dtype after max(v, 0)^2 (up == 1)
-// or as it is (up == 2: the activation is a kernel of its own); up == 3: x [slots, K] are sorted rows already (a gather
-// that also scaled them) and out [slots, N] is stored as it is in the compute dtype; else x [slots, K], out [slots, N] float32. w [experts, N, K]. max_tiles: the grid's height.
+// or as it is (up == 2: the activation is a kernel of its own); else x [slots, K], out [slots, N] float32. w [experts, N, K]. max_tiles: the grid's height.
 // 1 if row tiles of 64 are taken for these operands (the tensor-core form), else the plan must cut tiles of 32.
 TI_API int ti_moe_wide_tiles_ok(int K, int dtype) { return dtype == TI_BF16 && K % 8 == 0 ? 1 : 0; }
 
@@ -321,18 +324,16 @@ TI_API int ti_moe_gemm(void* out, const void* x, const void* w, const int* tiles
     typedef __nv_bfloat16 B;
     if (dtype == TI_F32) {
         if (up == 2) ti_launch(moe_gemm_kernel<float, float, true, false>, grid, EG_THREADS, 0, stream, (float*)out, (const float*)x, (const float*)w, tiles, num_tiles, token_of, N, K);
-        else if (up == 3) ti_launch(moe_gemm_kernel<float, float, false, false>, grid, EG_THREADS, 0, stream, (float*)out, (const float*)x, (const float*)w, tiles, num_tiles, token_of, N, K);
         else if (up) ti_launch(moe_gemm_kernel<float, float, true, true>, grid, EG_THREADS, 0, stream, (float*)out, (const float*)x, (const float*)w, tiles, num_tiles, token_of, N, K);
         else ti_launch(moe_gemm_kernel<float, float, false, false>, grid, EG_THREADS, 0, stream, (float*)out, (const float*)x, (const float*)w, tiles, num_tiles, token_of, N, K);
     } else if (tensor_cores) {
         dim3 mgrid((N + mt::BN - 1) / mt::BN, max_tiles);
 #define EG_MMA(O, G, R, MI) ti_launch(moe_gemm_mma_kernel<O, G, R, MI>, mgrid, mt::THREADS, 0, stream, (O*)out, (const B*)x, (const B*)w, tiles, num_tiles, token_of, N, K)
-        if (tile_rows == 64) { if (up == 2) EG_MMA(B, true, false, 4); else if (up == 3) EG_MMA(B, false, false, 4); else if (up) EG_MMA(B, true, true, 4); else EG_MMA(float, false, false, 4); }
-        else { if (up == 2) EG_MMA(B, true, false, 2); else if (up == 3) EG_MMA(B, false, false, 2); else if (up) EG_MMA(B, true, true, 2); else EG_MMA(float, false, false, 2); }
+        if (tile_rows == 64) { if (up == 2) EG_MMA(B, true, false, 4); else if (up) EG_MMA(B, true, true, 4); else EG_MMA(float, false, false, 4); }
+        else { if (up == 2) EG_MMA(B, true, false, 2); else if (up) EG_MMA(B, true, true, 2); else EG_MMA(float, false, false, 2); }
 #undef EG_MMA
     } else if (dtype == TI_BF16) {
         if (up == 2) ti_launch(moe_gemm_kernel<B, B, true, false>, grid, EG_THREADS, 0, stream, (B*)out, (const B*)x, (const B*)w, tiles, num_tiles, token_of, N, K);
-        else if (up == 3) ti_launch(moe_gemm_kernel<B, B, false, false>, grid, EG_THREADS, 0, stream, (B*)out, (const B*)x, (const B*)w, tiles, num_tiles, token_of, N, K);
         else if (up) ti_launch(moe_gemm_kernel<B, B, true, true>, grid, EG_THREADS, 0, stream, (B*)out, (const B*)x, (const B*)w, tiles, num_tiles, token_of, N, K);
         else ti_launch(moe_gemm_kernel<B, float, false, false>, grid, EG_THREADS, 0, stream, (float*)out, (const B*)x, (const B*)w, tiles, num_tiles, token_of, N, K);
     } else TI_REQUIRE(false, "moe_gemm: unknown dtype %d", dtype);
@@ -342,53 +343,28 @@ TI_API int ti_moe_gemm(void* out, const void* x, const void* w, const int* tiles
 
 // ------------------------------------------------------------------ rows into expert order
 // out[slot] = x[token_of[slot]]: the sorted copy that a product with tiled operand copies reads (a row a warp).
-// With slot_of and weight (both [tokens][top]): out[slot] = weight[token][choice] * x[token], the choice being the one
-// whose slot this is; the product in float32, one rounding.
 template <typename T>
-__global__ void moe_gather_kernel(T* __restrict__ out, const T* __restrict__ x, const int* __restrict__ token_of, int slots, int K,
-                                  const int* __restrict__ slot_of, const float* __restrict__ weight, int top) {
+__global__ void moe_gather_kernel(T* __restrict__ out, const T* __restrict__ x, const int* __restrict__ token_of, int slots, int K) {
     ti_grid_launch_dependents();
     ti_grid_wait();
     const int slot = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (slot >= slots) return;
-    const int token = token_of[slot];
-    const T* src = x + (size_t)token * K;
+    const T* src = x + (size_t)token_of[slot] * K;
     T* dst = out + (size_t)slot * K;
     constexpr int VEC = 16 / sizeof(T);
-    const bool wide = K % VEC == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)out & 15) == 0;
-    if (weight != nullptr) {
-        float f = 0.f;
-        for (int c = 0; c < top; ++c)
-            if (slot_of[(size_t)token * top + c] == slot) f = weight[(size_t)token * top + c];
-        if (wide) {
-            for (int i = lane; i < K / VEC; i += 32) {
-                uint4 raw = reinterpret_cast<const uint4*>(src)[i];
-                T* e = reinterpret_cast<T*>(&raw);
-#pragma unroll
-                for (int j = 0; j < VEC; ++j) e[j] = from_f32<T>(f * to_f32(e[j]));
-                reinterpret_cast<uint4*>(dst)[i] = raw;
-            }
-        } else {
-            for (int i = lane; i < K; i += 32) dst[i] = from_f32<T>(f * to_f32(src[i]));
-        }
-        return;
-    }
-    if (wide) {
+    if (K % VEC == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)out & 15) == 0) {
         for (int i = lane; i < K / VEC; i += 32) reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(src)[i];
     } else {
         for (int i = lane; i < K; i += 32) dst[i] = src[i];
     }
 }
 
-// slot_of and weight: both null (a plain gather) or both [tokens][top].
-TI_API int ti_moe_gather(void* out, const void* x, const int* token_of, int slots, int K, const int* slot_of,
-                         const float* weight, int top, int dtype, cudaStream_t stream) {
+TI_API int ti_moe_gather(void* out, const void* x, const int* token_of, int slots, int K, int dtype, cudaStream_t stream) {
     TI_REQUIRE(slots >= 0 && K > 0, "moe_gather: bad sizes");
-    TI_REQUIRE((slot_of == nullptr) == (weight == nullptr) && (weight == nullptr || top > 0), "moe_gather: weights come with the slots they belong to");
     if (slots == 0) return 0;
     const int blocks = (slots + 7) / 8;
-    if (dtype == TI_F32) ti_launch(moe_gather_kernel<float>, blocks, 256, 0, stream, (float*)out, (const float*)x, token_of, slots, K, slot_of, weight, top);
-    else if (dtype == TI_BF16) ti_launch(moe_gather_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)x, token_of, slots, K, slot_of, weight, top);
+    if (dtype == TI_F32) ti_launch(moe_gather_kernel<float>, blocks, 256, 0, stream, (float*)out, (const float*)x, token_of, slots, K);
+    else if (dtype == TI_BF16) ti_launch(moe_gather_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)x, token_of, slots, K);
     else TI_REQUIRE(false, "moe_gather: unknown dtype %d", dtype);
     TI_CHECK_LAUNCH("moe_gather");
     return 0;
@@ -478,28 +454,32 @@ TI_API int ti_moe_clamped_glu(void* out, const void* in, long long rows, int ff,
     return 0;
 }
 
-// in [rows][2 * ff] = [gate | up]; out [rows][ff] = silu(gate) * up, float32 arithmetic, one rounding.
+// in [rows][2 * ff] = [gate | up]; out [rows][ff] = silu(s gate) * (s up) with s = row_scale[row] (1 without it), float32
+// arithmetic, one rounding.
 template <typename T>
-__global__ void moe_silu_glu_kernel(T* __restrict__ out, const T* __restrict__ in, size_t rows, int ff) {
+__global__ void moe_silu_glu_kernel(T* __restrict__ out, const T* __restrict__ in, size_t rows, int ff,
+                                    const float* __restrict__ row_scale) {
     ti_grid_launch_dependents();
     ti_grid_wait();
     const size_t n = rows * ff, stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride) {
         const size_t r = i / ff;
         const int c = (int)(i % ff);
-        const float g = to_f32(in[r * 2 * ff + c]);
-        const float u = to_f32(in[r * 2 * ff + ff + c]);
+        const float s = row_scale ? row_scale[r] : 1.f;
+        const float g = s * to_f32(in[r * 2 * ff + c]);
+        const float u = s * to_f32(in[r * 2 * ff + ff + c]);
         out[i] = from_f32<T>(g / (1.f + expf(-g)) * u);
     }
 }
 
-TI_API int ti_moe_silu_glu(void* out, const void* in, long long rows, int ff, int dtype, cudaStream_t stream) {
+TI_API int ti_moe_silu_glu(void* out, const void* in, long long rows, int ff, const float* row_scale, int dtype,
+                           cudaStream_t stream) {
     TI_REQUIRE(rows >= 0 && ff > 0, "moe_silu_glu: bad sizes");
     if (rows == 0) return 0;
     const long long want = (rows * ff + 255) / 256;
     const int blocks = (int)(want < 148 * 16 ? want : 148 * 16);
-    if (dtype == TI_F32) ti_launch(moe_silu_glu_kernel<float>, blocks, 256, 0, stream, (float*)out, (const float*)in, (size_t)rows, ff);
-    else if (dtype == TI_BF16) ti_launch(moe_silu_glu_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)in, (size_t)rows, ff);
+    if (dtype == TI_F32) ti_launch(moe_silu_glu_kernel<float>, blocks, 256, 0, stream, (float*)out, (const float*)in, (size_t)rows, ff, row_scale);
+    else if (dtype == TI_BF16) ti_launch(moe_silu_glu_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)in, (size_t)rows, ff, row_scale);
     else TI_REQUIRE(false, "moe_silu_glu: unknown dtype %d", dtype);
     TI_CHECK_LAUNCH("moe_silu_glu");
     return 0;

@@ -74,14 +74,14 @@ _SIGNATURES = {
     # routed experts
     "experts": {
         "ti_moe_route": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                         c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                         c_void_p],
+                         c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int,
+                         c_int, c_void_p],
         "ti_moe_tile_rows": [],
         "ti_moe_gemm": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                         c_void_p],
         "ti_moe_wide_tiles_ok": [c_int, c_int],
-        "ti_moe_gather": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p],
-        "ti_moe_silu_glu": [c_void_p, c_void_p, c_ll, c_int, c_int, c_void_p],
+        "ti_moe_gather": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+        "ti_moe_silu_glu": [c_void_p, c_void_p, c_ll, c_int, c_void_p, c_int, c_void_p],
         "ti_moe_combine_norm_add": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
                                     c_int, c_float, c_int, c_void_p],
         "ti_moe_clamped_glu": [c_void_p, c_void_p, c_ll, c_int, c_float, c_float, c_int, c_void_p],
@@ -1008,12 +1008,13 @@ class ExpertRouting:
     """Where a step's tokens go: ``chosen`` int32 [T, top], ``weight`` float32 [T, top], ``slot_of`` int32 [T, top]
     (row of each (token, choice) in the order sorted by expert), ``token_of`` int32 [T * top], and the row tiles
     ``tiles`` int32 [max_tiles, 3] = [expert, first row, rows] with their count ``num_tiles`` int32 [1] (on the
-    device: the grouped products are launched for ``max_tiles`` and the surplus returns at once)."""
+    device: the grouped products are launched for ``max_tiles`` and the surplus returns at once). ``slot_weight``
+    float32 [T * top]: the weights in the sorted order (row ``slot_of[t, c]`` holds ``weight[t, c]``)."""
 
-    def __init__(self, chosen, weight, slot_of, token_of, tiles, num_tiles, max_tiles, counts, tile_rows):
+    def __init__(self, chosen, weight, slot_of, token_of, tiles, num_tiles, max_tiles, counts, tile_rows, slot_weight=None):
         self.chosen, self.weight, self.slot_of, self.token_of = chosen, weight, slot_of, token_of
         self.tiles, self.num_tiles, self.max_tiles, self.counts = tiles, num_tiles, max_tiles, counts
-        self.tile_rows = tile_rows
+        self.tile_rows, self.slot_weight = tile_rows, slot_weight
 
 
 def route_experts(x32: torch.Tensor, w_router: torch.Tensor, top: int, weight_eps: float,
@@ -1053,14 +1054,15 @@ def route_experts(x32: torch.Tensor, w_router: torch.Tensor, top: int, weight_ep
     counts, starts = ints[o:o + experts], ints[o + experts:o + 2 * experts + 1]
     o += 2 * experts + 1
     tiles, num_tiles = ints[o:o + 3 * max_tiles], ints[o + 3 * max_tiles:o + 3 * max_tiles + 1]
-    weight = torch.empty((t, top), dtype=torch.float32, device=dev)
+    both = torch.empty((2, t, top), dtype=torch.float32, device=dev)
+    weight, slot_weight = both[0], both[1].view(-1)
     _run("experts", "ti_moe_route", chosen.data_ptr(), weight.data_ptr(), rank.data_ptr(), counts.data_ptr(),
          starts.data_ptr(), tiles.data_ptr(), num_tiles.data_ptr(), slot_of.data_ptr(), token_of.data_ptr(),
          x32.data_ptr(), w_router.data_ptr(), t, hidden, experts, top, float(weight_eps), _ptr(correction),
-         int(renormalize), real, tile_rows, max_tiles, int(scoring == "sigmoid"), _dtype_code(x32), _dtype_code(w_router),
-         _stream())
+         int(renormalize), real, tile_rows, max_tiles, int(scoring == "sigmoid"), slot_weight.data_ptr(), _dtype_code(x32),
+         _dtype_code(w_router), _stream())
     return ExpertRouting(chosen.view(t, top), weight, slot_of.view(t, top), token_of, tiles.view(max_tiles, 3),
-                         num_tiles, max_tiles, counts, tile_rows)
+                         num_tiles, max_tiles, counts, tile_rows, slot_weight)
 
 
 def expert_tiles_may_be_wide(x: torch.Tensor, *inner_sizes: int) -> bool:
@@ -1085,13 +1087,11 @@ def expert_tile_rows(x: torch.Tensor, num_experts: int, top: int, *inner_sizes: 
     return int(_fn("experts", "ti_moe_tile_rows")())
 
 
-def expert_linear(x: torch.Tensor, w: torch.Tensor, routing: ExpertRouting, *, up: bool, activation: bool = True,
-                  weighted_input: bool = False) -> torch.Tensor:
+def expert_linear(x: torch.Tensor, w: torch.Tensor, routing: ExpertRouting, *, up: bool, activation: bool = True) -> torch.Tensor:
     """Grouped product over the routing's row tiles with ``w`` [E, N, K]. ``up``: ``x`` [T, K] are the step's
     tokens, gathered per expert; the result [T * top, N] (sorted rows) has passed max(v, 0)^2 (``activation``
     False: it is stored as it is, for an activation that is a kernel of its own). Otherwise ``x``
-    are sorted rows [T * top, K] and the result is float32 [T * top, N]. ``weighted_input`` (with ``up``): the row
-    an expert reads is the token's row times the weight of that (token, choice), rounded once."""
+    are sorted rows [T * top, K] and the result is float32 [T * top, N]."""
     _check(x, "x", None, 2)
     _check(w, "w", x.dtype, 3)
     _, n, k = w.shape
@@ -1100,26 +1100,16 @@ def expert_linear(x: torch.Tensor, w: torch.Tensor, routing: ExpertRouting, *, u
     slots = routing.token_of.shape[0]
     out = torch.empty((slots, n), dtype=x.dtype if up else torch.float32, device=x.device)
     form = (1 if activation else 2) if up else 0
-    if weighted_input and not (up and not activation):
-        raise KernelError("expert_linear: weighted rows enter an up product whose activation is a kernel of its own")
-
-    def gathered(weights: bool) -> torch.Tensor:
-        rows = torch.empty((slots, k), dtype=x.dtype, device=x.device)
-        _run("experts", "ti_moe_gather", rows.data_ptr(), x.data_ptr(), routing.token_of.data_ptr(), slots, k,
-             routing.slot_of.data_ptr() if weights else None, routing.weight.data_ptr() if weights else None,
-             routing.chosen.shape[1], _dtype_code(x), _stream())
-        return rows
-
     if routing.tile_rows == 128:                 # tcgen05: tiled operand copies want the rows in expert order
         rows = x
         if up:
-            rows = gathered(weighted_input)
+            rows = torch.empty((slots, k), dtype=x.dtype, device=x.device)
+            _run("experts", "ti_moe_gather", rows.data_ptr(), x.data_ptr(), routing.token_of.data_ptr(), slots, k,
+                 _dtype_code(x), _stream())
         _run("sm100", "ti_moe_gemm_tcgen05", out.data_ptr(), rows.data_ptr(), w.data_ptr(), routing.tiles.data_ptr(),
              routing.num_tiles.data_ptr(), slots, w.shape[0], n, k, routing.max_tiles, form,
              kernel_status(x.device).data_ptr(), _stream())
         return out
-    if weighted_input:                           # the rows are scaled while they are put in expert order
-        x, form = gathered(True), 3
     _run("experts", "ti_moe_gemm", out.data_ptr(), x.data_ptr(), w.data_ptr(), routing.tiles.data_ptr(),
          routing.num_tiles.data_ptr(), routing.token_of.data_ptr(), n, k, routing.max_tiles, routing.tile_rows, form,
          _dtype_code(x), _stream())
@@ -1158,15 +1148,21 @@ def clamped_glu(gate_up: torch.Tensor, limit: float, alpha: float) -> torch.Tens
     return out
 
 
-def silu_glu(gate_up: torch.Tensor) -> torch.Tensor:
+def silu_glu(gate_up: torch.Tensor, row_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
     """silu(gate) * up on a stored product ``gate_up`` [rows, 2 F] = [gate | up] -> [rows, F]; float32 arithmetic, one
-    rounding."""
+    rounding. ``row_scale`` float32 [rows]: both halves of a row are multiplied by its number first, silu(s gate) * (s up):
+    for experts that are weighted at their input, since W (s h) = s (W h) (``ExpertRouting.slot_weight``)."""
     _check(gate_up, "gate_up", None, 2)
     rows, two_f = gate_up.shape
     if two_f % 2:
         raise KernelError("silu_glu: a row holds a gate half and an up half")
+    if row_scale is not None:
+        _check(row_scale, "row_scale", torch.float32, 1)
+        if row_scale.shape[0] != rows:
+            raise KernelError("silu_glu: one number per row")
     out = torch.empty((rows, two_f // 2), dtype=gate_up.dtype, device=gate_up.device)
-    _run("experts", "ti_moe_silu_glu", out.data_ptr(), gate_up.data_ptr(), rows, two_f // 2, _dtype_code(gate_up), _stream())
+    _run("experts", "ti_moe_silu_glu", out.data_ptr(), gate_up.data_ptr(), rows, two_f // 2, _ptr(row_scale),
+         _dtype_code(gate_up), _stream())
     return out
 
 

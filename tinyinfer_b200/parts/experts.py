@@ -9,8 +9,8 @@ g = min(W_gate h, limit), u = clamp(W_up h, -limit, limit), down(g * sigmoid(alp
 weights are the chosen scores themselves) and ``router_input`` 'input' (the router reads the sublayer's normed input
 instead of the float32 stream), ``activation`` 'silu_glu' (down(silu(W_gate h) * (W_up h))), ``scoring`` 'sigmoid' (an
 expert's score is the sigmoid of its own router logit) and ``weight_input`` (a chosen expert runs on its weight times
-the token's row, expert(w h), and the outputs are summed as they are: the rows are scaled as they are put in expert
-order).
+the token's row, expert(w h), and the outputs are summed as they are: the up product is linear, W (w h) = w (W h), so
+the weight multiplies both halves of the stored product inside the activation kernel and costs no pass of its own).
 
 A step's (token, choice) pairs are put in expert order on the device and the experts run as two grouped
 products over row tiles; nothing is read back to the host and no token is ever dropped, so a token's result
@@ -35,8 +35,8 @@ class Experts(FeedForward):
             raise ValueError(f"activation {spec.activation!r} is not supported (relu_squared, clamped_glu, silu_glu)")
         if spec.scoring not in ("softmax", "sigmoid"):
             raise ValueError(f"scoring {spec.scoring!r} is not supported (softmax, sigmoid)")
-        if spec.weight_input and (spec.activation == "relu_squared" or spec.identity_experts or spec.shared_size):
-            raise ValueError("experts weighted at their input are gated ones, without identity or shared experts")
+        if spec.weight_input and (spec.activation != "silu_glu" or spec.identity_experts or spec.shared_size):
+            raise ValueError("experts weighted at their input are silu-gated ones, without identity or shared experts")
         if spec.activation == "clamped_glu" and not spec.glu_limit > 0:
             raise ValueError("clamped_glu needs a positive limit")
         if spec.identity_experts < 0 or spec.top > spec.num_experts + spec.identity_experts:
@@ -86,8 +86,8 @@ class Experts(FeedForward):
                                     correction=self.correction, renormalize=s.renormalize, real_experts=s.num_experts,
                                     scoring=s.scoring)
         if self.glu:
-            gate_up = ops.expert_linear(x, self.w_up, routing, up=True, activation=False, weighted_input=s.weight_input)
-            hidden = (ops.silu_glu(gate_up) if s.activation == "silu_glu"
+            gate_up = ops.expert_linear(x, self.w_up, routing, up=True, activation=False)
+            hidden = (ops.silu_glu(gate_up, routing.slot_weight if s.weight_input else None) if s.activation == "silu_glu"
                       else ops.clamped_glu(gate_up, s.glu_limit, s.glu_alpha))
         else:
             hidden = ops.expert_linear(x, self.w_up, routing, up=True)
